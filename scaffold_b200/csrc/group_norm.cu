@@ -1,0 +1,451 @@
+// GroupNorm (+ fused ReLU) for channels-last bf16 activations, forward and
+// backward, with statistics that can span several spatial shards.
+//
+// Forward, two streaming passes (3 tensor-volumes of traffic):
+//   gn_stats_kernel     per (split, n) CTA: Welford-style (count, mean, M2)
+//                       partials for all G groups over a contiguous voxel range
+//   gn_apply_kernel     every CTA merges the partials of its sample in index
+//                       order (Chan's formula; deterministic), then
+//                       y = relu((x - mean) * rstd * w + b), stored in bf16
+// Backward, two streaming passes (5 volumes):
+//   gn_bwd_partial      per (split, n): per-channel sum(dy') and sum(dy' * xhat),
+//                       dy' = dy gated by the recomputed ReLU mask
+//   gn_bwd_dx           merges partials, dx = rstd * (dy' w - c1 - xhat c2);
+//                       CTA (0,0) also reduces dweight / dbias over samples
+//
+// "Peer" partial blocks: both merge steps walk `n_parts` partial buffers (this
+// rank's first, then its spatial neighbours' through peer pointers), which
+// makes a sharded volume normalise exactly like the unsharded one.
+//
+// Every thread owns 8 consecutive channels (one 16-byte vector) of a voxel, so
+// all global accesses are full coalesced 16-byte vectors.
+//
+// Role of the reference: ScaFFold/unet/triton_group_norm.py:594-1043.
+#include "common.cuh"
+#include "host_api.h"
+
+namespace sb {
+
+constexpr int GN_THREADS = 256;
+constexpr int GN_MAX_PARTS = 8;
+
+struct GnParams {
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* dy;
+  __nv_bfloat16* y;   // forward output / backward dx
+  const float* w;
+  const float* b;
+  float* mean;   // [N, G]
+  float* rstd;   // [N, G]
+  float* part;   // this rank's partials
+  const float* parts[GN_MAX_PARTS];  // partial buffers to merge (own first)
+  int n_parts;
+  float* dw;     // [C]
+  float* db;     // [C]
+  int N, C, G;
+  long long S;   // voxels per sample (local shard)
+  int nsplit;
+  float eps;
+  int relu;
+  float group_elems;  // elements per (n, g) over ALL shards = S_total * C/G
+};
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 o;
+  o.x = pack_bf16x2(f[0], f[1]);
+  o.y = pack_bf16x2(f[2], f[3]);
+  o.z = pack_bf16x2(f[4], f[5]);
+  o.w = pack_bf16x2(f[6], f[7]);
+  return o;
+}
+
+__device__ __forceinline__ void chan_merge(float& n_a, float& mean_a, float& m2_a, float n_b, float mean_b,
+                                           float m2_b) {
+  if (n_b == 0.f) return;
+  const float n = n_a + n_b;
+  const float delta = mean_b - mean_a;
+  const float r = n_b / n;
+  mean_a += delta * r;
+  m2_a += m2_b + delta * delta * n_a * r;
+  n_a = n;
+}
+
+// ----------------------------------------------------------------------------
+// forward: statistics
+// ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(GN_THREADS) gn_stats_kernel(const GnParams p) {
+  __shared__ float s_n[GN_THREADS * 4], s_mean[GN_THREADS * 4], s_m2[GN_THREADS * 4];
+  const int split = blockIdx.x, n = blockIdx.y;
+  const int tpv = p.C / 8;            // threads per voxel
+  const int vpb = GN_THREADS / tpv;   // voxels per block iteration
+  const int oct = threadIdx.x % tpv;
+  const int vl = threadIdx.x / tpv;
+  const int cg = p.C / p.G;
+  const long long chunk = (p.S + p.nsplit - 1) / p.nsplit;
+  const long long v0 = (long long)split * chunk;
+  const long long v1 = v0 + chunk < p.S ? v0 + chunk : p.S;
+  const __nv_bfloat16* xb = p.x + (long long)n * p.S * p.C + oct * 8;
+
+  float s[8], q[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { s[i] = 0.f; q[i] = 0.f; }
+  float cnt = 0.f;
+  // first value of the thread is the shift: sums of (x - shift) stay small
+  float shift[8];
+  bool have_shift = false;
+  if (vl < vpb) {
+    for (long long v = v0 + vl; v < v1; v += vpb) {
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xb + v * p.C));
+      float f[8];
+      unpack8(raw, f);
+      if (!have_shift) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) shift[i] = f[i];
+        have_shift = true;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float d = f[i] - shift[i];
+        s[i] += d;
+        q[i] += d * d;
+      }
+      cnt += 1.f;
+    }
+  }
+  // per-thread (count, mean, M2) for each group it touches (ngt = max(1, 8/cg) groups)
+  const int ngt = cg >= 8 ? 1 : 8 / cg;
+  const int cpg = 8 / ngt;  // channels of this thread per group
+  for (int gi = 0; gi < ngt; ++gi) {
+    float gn = 0.f, gm = 0.f, g2 = 0.f;
+    if (cnt > 0.f) {
+      for (int j = 0; j < cpg; ++j) {
+        const int i = gi * cpg + j;
+        const float m = s[i] / cnt;
+        const float m2 = fmaxf(q[i] - s[i] * m, 0.f);
+        chan_merge(gn, gm, g2, cnt, m + shift[i], m2);
+      }
+    }
+    s_n[threadIdx.x * 4 + gi] = gn;
+    s_mean[threadIdx.x * 4 + gi] = gm;
+    s_m2[threadIdx.x * 4 + gi] = g2;
+  }
+  __syncthreads();
+  // one thread per group merges that group's entries in thread order
+  if (threadIdx.x < p.G) {
+    const int g = threadIdx.x;
+    float gn = 0.f, gm = 0.f, g2 = 0.f;
+    // channels of group g: [g*cg, (g+1)*cg) -> octs [g*cg/8, ...]
+    const int oct0 = (g * cg) / 8;
+    const int octs = cg >= 8 ? cg / 8 : 1;
+    const int gi = cg >= 8 ? 0 : (g * cg % 8) / cg;
+    for (int v = 0; v < vpb; ++v)
+      for (int o = 0; o < octs; ++o) {
+        const int t = v * tpv + oct0 + o;
+        chan_merge(gn, gm, g2, s_n[t * 4 + gi], s_mean[t * 4 + gi], s_m2[t * 4 + gi]);
+      }
+    float* dst = p.part + (((long long)n * p.nsplit + split) * p.G + g) * 3;
+    dst[0] = gn;
+    dst[1] = gm;
+    dst[2] = g2;
+  }
+}
+
+// merges every partial of sample n, group g, in (part buffer, split) order
+__device__ __forceinline__ void merge_group(const GnParams& p, int n, int g, float& mean, float& rstd) {
+  float gn = 0.f, gm = 0.f, g2 = 0.f;
+  for (int pi = 0; pi < p.n_parts; ++pi) {
+    const float* base = p.parts[pi] + ((long long)n * p.nsplit * p.G + g) * 3;
+    for (int s = 0; s < p.nsplit; ++s) {
+      const float* e = base + (long long)s * p.G * 3;
+      chan_merge(gn, gm, g2, e[0], e[1], e[2]);
+    }
+  }
+  mean = gm;
+  rstd = rsqrtf(g2 / gn + p.eps);
+}
+
+// ----------------------------------------------------------------------------
+// forward: normalise + affine + ReLU
+// ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(GN_THREADS) gn_apply_kernel(const GnParams p) {
+  __shared__ float s_mean[256], s_rstd[256];
+  const int n = blockIdx.y;
+  for (int g = threadIdx.x; g < p.G; g += GN_THREADS) {
+    float m, r;
+    merge_group(p, n, g, m, r);
+    s_mean[g] = m;
+    s_rstd[g] = r;
+    if (blockIdx.x == 0) {
+      p.mean[n * p.G + g] = m;
+      p.rstd[n * p.G + g] = r;
+    }
+  }
+  __syncthreads();
+  const int tpv = p.C / 8;
+  const int vpb = GN_THREADS / tpv;
+  const int oct = threadIdx.x % tpv;
+  const int vl = threadIdx.x / tpv;
+  if (vl >= vpb) return;
+  const int cg = p.C / p.G;
+  float a[8], c[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int ch = oct * 8 + i;
+    const int g = ch / cg;
+    a[i] = s_rstd[g] * p.w[ch];
+    c[i] = p.b[ch] - s_mean[g] * a[i];
+  }
+  const long long base = (long long)n * p.S * p.C + oct * 8;
+  for (long long v = (long long)blockIdx.x * vpb + vl; v < p.S; v += (long long)gridDim.x * vpb) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p.x + base + v * p.C));
+    float f[8];
+    unpack8(raw, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float yv = fmaf(f[i], a[i], c[i]);
+      if (p.relu) yv = yv <= 0.f ? 0.f : yv;  // NaN propagates
+      f[i] = yv;
+    }
+    *reinterpret_cast<uint4*>(p.y + base + v * p.C) = pack8(f);
+  }
+}
+
+// ----------------------------------------------------------------------------
+// backward: per-channel partial sums
+// ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(GN_THREADS) gn_bwd_partial_kernel(const GnParams p) {
+  __shared__ float s_a[GN_THREADS * 8], s_b[GN_THREADS * 8];
+  const int split = blockIdx.x, n = blockIdx.y;
+  const int tpv = p.C / 8;
+  const int vpb = GN_THREADS / tpv;
+  const int oct = threadIdx.x % tpv;
+  const int vl = threadIdx.x / tpv;
+  const int cg = p.C / p.G;
+  const long long chunk = (p.S + p.nsplit - 1) / p.nsplit;
+  const long long v0 = (long long)split * chunk;
+  const long long v1 = v0 + chunk < p.S ? v0 + chunk : p.S;
+  float mu[8], rs[8], wv[8], bv[8], A[8], B[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int ch = oct * 8 + i;
+    const int g = ch / cg;
+    mu[i] = p.mean[n * p.G + g];
+    rs[i] = p.rstd[n * p.G + g];
+    wv[i] = p.w[ch];
+    bv[i] = p.b[ch];
+    A[i] = 0.f;
+    B[i] = 0.f;
+  }
+  const long long base = (long long)n * p.S * p.C + oct * 8;
+  if (vl < vpb) {
+    for (long long v = v0 + vl; v < v1; v += vpb) {
+      const uint4 rx = __ldg(reinterpret_cast<const uint4*>(p.x + base + v * p.C));
+      const uint4 rd = __ldg(reinterpret_cast<const uint4*>(p.dy + base + v * p.C));
+      float fx[8], fd[8];
+      unpack8(rx, fx);
+      unpack8(rd, fd);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xh = (fx[i] - mu[i]) * rs[i];
+        float d = fd[i];
+        if (p.relu && fmaf(xh, wv[i], bv[i]) <= 0.f) d = 0.f;
+        A[i] += d;
+        B[i] += d * xh;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    s_a[threadIdx.x * 8 + i] = A[i];
+    s_b[threadIdx.x * 8 + i] = B[i];
+  }
+  __syncthreads();
+  for (int ch = threadIdx.x; ch < p.C; ch += GN_THREADS) {
+    const int o = ch / 8, j = ch % 8;
+    float sa = 0.f, sbv = 0.f;
+    for (int v = 0; v < vpb; ++v) {
+      const int t = v * tpv + o;
+      sa += s_a[t * 8 + j];
+      sbv += s_b[t * 8 + j];
+    }
+    float* dst = p.part + (((long long)n * p.nsplit + split) * p.C + ch) * 2;
+    dst[0] = sa;
+    dst[1] = sbv;
+  }
+}
+
+// ----------------------------------------------------------------------------
+// backward: dx (+ dweight / dbias)
+// ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(GN_THREADS) gn_bwd_dx_kernel(const GnParams p) {
+  extern __shared__ float sm[];
+  float* s_A = sm;              // [C] this rank's sum(dy')
+  float* s_B = sm + p.C;        // [C] this rank's sum(dy' xhat)
+  float* s_c1 = sm + 2 * p.C;   // [G]
+  float* s_c2 = s_c1 + p.G;     // [G]
+  float* s_At = s_c2 + p.G;     // [C] all shards
+  float* s_Bt = s_At + p.C;
+  const int n = blockIdx.y;
+  const int cg = p.C / p.G;
+  for (int ch = threadIdx.x; ch < p.C; ch += GN_THREADS) {
+    float At = 0.f, Bt = 0.f, A0 = 0.f, B0 = 0.f;
+    for (int pi = 0; pi < p.n_parts; ++pi) {
+      const float* base = p.parts[pi] + ((long long)n * p.nsplit * p.C + ch) * 2;
+      float a = 0.f, b = 0.f;
+      for (int s = 0; s < p.nsplit; ++s) {
+        a += base[(long long)s * p.C * 2];
+        b += base[(long long)s * p.C * 2 + 1];
+      }
+      if (pi == 0) { A0 = a; B0 = b; }
+      At += a;
+      Bt += b;
+    }
+    s_A[ch] = A0; s_B[ch] = B0; s_At[ch] = At; s_Bt[ch] = Bt;
+  }
+  __syncthreads();
+  for (int g = threadIdx.x; g < p.G; g += GN_THREADS) {
+    float c1 = 0.f, c2 = 0.f;
+    for (int j = 0; j < cg; ++j) {
+      const int ch = g * cg + j;
+      c1 += p.w[ch] * s_At[ch];
+      c2 += p.w[ch] * s_Bt[ch];
+    }
+    s_c1[g] = c1 / p.group_elems;
+    s_c2[g] = c2 / p.group_elems;
+  }
+  __syncthreads();
+  // dweight / dbias: this rank's share, summed over samples in index order
+  if (blockIdx.x == 0 && blockIdx.y == 0 && p.dw != nullptr) {
+    for (int ch = threadIdx.x; ch < p.C; ch += GN_THREADS) {
+      float a = 0.f, b = 0.f;
+      for (int nn = 0; nn < p.N; ++nn) {
+        const float* base = p.parts[0] + ((long long)nn * p.nsplit * p.C + ch) * 2;
+        for (int s = 0; s < p.nsplit; ++s) {
+          a += base[(long long)s * p.C * 2];
+          b += base[(long long)s * p.C * 2 + 1];
+        }
+      }
+      p.db[ch] = a;
+      p.dw[ch] = b;
+    }
+  }
+  const int tpv = p.C / 8;
+  const int vpb = GN_THREADS / tpv;
+  const int oct = threadIdx.x % tpv;
+  const int vl = threadIdx.x / tpv;
+  if (vl >= vpb) return;
+  float mu[8], rs[8], wv[8], bv[8], c1[8], c2[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int ch = oct * 8 + i;
+    const int g = ch / cg;
+    mu[i] = p.mean[n * p.G + g];
+    rs[i] = p.rstd[n * p.G + g];
+    wv[i] = p.w[ch];
+    bv[i] = p.b[ch];
+    c1[i] = s_c1[g];
+    c2[i] = s_c2[g];
+  }
+  const long long base = (long long)n * p.S * p.C + oct * 8;
+  for (long long v = (long long)blockIdx.x * vpb + vl; v < p.S; v += (long long)gridDim.x * vpb) {
+    const uint4 rx = __ldg(reinterpret_cast<const uint4*>(p.x + base + v * p.C));
+    const uint4 rd = __ldg(reinterpret_cast<const uint4*>(p.dy + base + v * p.C));
+    float fx[8], fd[8];
+    unpack8(rx, fx);
+    unpack8(rd, fd);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float xh = (fx[i] - mu[i]) * rs[i];
+      float d = fd[i];
+      if (p.relu && fmaf(xh, wv[i], bv[i]) <= 0.f) d = 0.f;
+      fx[i] = rs[i] * (d * wv[i] - c1[i] - xh * c2[i]);
+    }
+    *reinterpret_cast<uint4*>(p.y + base + v * p.C) = pack8(fx);
+  }
+}
+
+static int gn_fill(const SbGnArgs* a, GnParams& p) {
+  if (a->C % 8 != 0 || a->C % a->G != 0 || a->C > 2048 || a->G > 256) return SB_ERR_SHAPE;
+  const int cg = a->C / a->G;
+  if (cg < 8 ? (8 % cg != 0) : (cg % 8 != 0)) return SB_ERR_SHAPE;
+  if (a->C / 8 > GN_THREADS || (cg < 8 && 8 / cg > 4)) return SB_ERR_SHAPE;
+  if (a->n_parts < 1 || a->n_parts > GN_MAX_PARTS) return SB_ERR_SHAPE;
+  memset(&p, 0, sizeof(p));
+  p.x = (const __nv_bfloat16*)a->x;
+  p.dy = (const __nv_bfloat16*)a->dy;
+  p.y = (__nv_bfloat16*)a->y;
+  p.w = a->w; p.b = a->b; p.mean = a->mean; p.rstd = a->rstd;
+  p.part = a->part;
+  for (int i = 0; i < a->n_parts; ++i) p.parts[i] = a->parts[i];
+  p.n_parts = a->n_parts;
+  p.dw = a->dw; p.db = a->db;
+  p.N = a->N; p.C = a->C; p.G = a->G; p.S = a->S;
+  p.nsplit = a->nsplit;
+  p.eps = a->eps;
+  p.relu = a->relu;
+  p.group_elems = (float)((double)a->S_total * cg);
+  return 0;
+}
+
+static int apply_blocks(const GnParams& p) {
+  const int vpb = GN_THREADS / (p.C / 8);
+  long long need = (p.S + vpb - 1) / vpb;
+  long long cap = (148LL * 8 + p.N - 1) / p.N;
+  long long b = need < cap ? need : cap;
+  return (int)(b < 1 ? 1 : b);
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" int sb_gn_nsplit(int N, long long S, int C) {
+  const int vpb = GN_THREADS / (C / 8);
+  long long maxs = (S + vpb - 1) / vpb;  // at least one row of voxels per split
+  long long want = (148LL * 4 + N - 1) / N;
+  long long s = want < maxs ? want : maxs;
+  if (s > 1024) s = 1024;
+  return (int)(s < 1 ? 1 : s);
+}
+
+extern "C" int sb_gn_stats(const SbGnArgs* a, cudaStream_t stream) {
+  GnParams p;
+  int rc = gn_fill(a, p);
+  if (rc) return rc;
+  gn_stats_kernel<<<dim3(p.nsplit, p.N), GN_THREADS, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
+extern "C" int sb_gn_apply(const SbGnArgs* a, cudaStream_t stream) {
+  GnParams p;
+  int rc = gn_fill(a, p);
+  if (rc) return rc;
+  gn_apply_kernel<<<dim3(apply_blocks(p), p.N), GN_THREADS, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
+extern "C" int sb_gn_bwd_partial(const SbGnArgs* a, cudaStream_t stream) {
+  GnParams p;
+  int rc = gn_fill(a, p);
+  if (rc) return rc;
+  gn_bwd_partial_kernel<<<dim3(p.nsplit, p.N), GN_THREADS, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
+extern "C" int sb_gn_bwd_dx(const SbGnArgs* a, cudaStream_t stream) {
+  GnParams p;
+  int rc = gn_fill(a, p);
+  if (rc) return rc;
+  const size_t smem = (size_t)(4 * p.C + 2 * p.G) * sizeof(float);
+  gn_bwd_dx_kernel<<<dim3(apply_blocks(p), p.N), GN_THREADS, smem, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}

@@ -1,0 +1,84 @@
+// C ABI of libscaffold_b200.so. Every entry point takes raw device pointers and
+// a CUDA stream, allocates nothing and returns 0 or an SB_ERR_* code; the
+// Python layer (scaffold_b200/ops/_lib.py) mirrors these structs with ctypes.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  SB_OK = 0,
+  SB_ERR_DRIVER = 1,     // could not resolve / call the driver entry point
+  SB_ERR_ALIGN = 2,      // pointer or stride violates a TMA alignment rule
+  SB_ERR_TENSORMAP = 3,  // cuTensorMapEncodeTiled refused the description
+  SB_ERR_SHAPE = 4,      // shape outside what the kernel supports
+  SB_ERR_LAUNCH = 5,     // launch error
+  SB_ERR_TOO_LARGE = 6,  // request exceeds a fixed capacity
+};
+
+// stride-1 "same" convolution (k = 1 or 3) over up to two channel-concatenated
+// NDHWC bf16 sources into up to two channel-split NDHWC bf16 destinations
+typedef struct {
+  const void* src[2];
+  int src_c[2];   // channels read from each source (src_c[1] = 0: one source)
+  int src_ld[2];  // channel stride (elements per voxel) of each source
+  int N, D, H, W;
+  int ksize;
+  const void* wpack;  // bf16 [taps][cout_pad][cin_total], taps ordered (kd,kh,kw)
+  int cout_pad;       // rows per tap in wpack (multiple of 16)
+  void* dst[2];
+  int dst_c[2];   // channels stored into each destination (multiples of 8)
+  int dst_ld[2];  // channel stride of each destination
+  const float* bias;  // optional, added to destination 0 columns
+  uint32_t* status;   // optional 4-word status block
+  int force_plain;    // tests: disable the w-shift reuse path
+} SbConvArgs;
+
+// k=2,s=2 transposed convolution. Forward: src [N,D,H,W,cin] -> dst
+// [N,2D,2H,2W,cout], wpack bf16 [8*cout][cin] (row = tap*cout + co).
+// Backward-data (sb_convT_dgrad): src = gy [N,2D,2H,2W,cout] -> dst = gx
+// [N,D,H,W,cin], wpack bf16 [4][wrows][2*cout] (outer = kd*2+kh, col = kw*cout+co).
+typedef struct {
+  const void* src;
+  int src_ld;
+  int N, D, H, W;  // the COARSE grid (input of forward / output of dgrad)
+  int cin, cout;
+  const void* wpack;
+  int wrows;  // dgrad: rows per outer tap in wpack (cin padded to a multiple of 16)
+  void* dst;
+  int dst_ld;
+  const float* bias;
+  uint32_t* status;
+} SbConvTArgs;
+
+// Weight gradient: out[g][m][j] (fp32) = sum_voxels A[voxel, m] * B_g,j[voxel', n(j)]
+// with deterministic split-K partials in `workspace` reduced by sb_wgrad_reduce.
+typedef struct {
+  const void* gy;  // NDHWC bf16 gradient w.r.t. conv output, [N,D,H,W,gy_ld]
+  int gy_c, gy_ld;
+  const void* x[2];  // NDHWC bf16 conv inputs (two when the input was a fused concat)
+  int x_c[2], x_ld[2];
+  int N, D, H, W;
+  int ksize;          // 1 or 3 (same conv) ; 2 = k2s2 transposed (gy is the fine grid)
+  float* workspace;   // fp32 [splits][taps][gy_c or M][cin_total]
+  long long workspace_elems;
+  float* dw;          // fp32 gradient in the parameter's own layout
+  int dw_cout, dw_cin;  // real (unpadded) channel counts of the parameter
+  int accumulate;     // add into dw instead of overwriting
+  uint32_t* status;
+  int splits;         // 0: choose
+} SbWgradArgs;
+
+int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream);
+int sb_convT_fwd(const SbConvTArgs* a, cudaStream_t stream);
+int sb_convT_dgrad(const SbConvTArgs* a, cudaStream_t stream);
+int sb_conv_wgrad(const SbWgradArgs* a, cudaStream_t stream);
+long long sb_conv_wgrad_workspace(const SbWgradArgs* a);
+
+#ifdef __cplusplus
+}
+#endif

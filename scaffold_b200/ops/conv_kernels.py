@@ -1,0 +1,200 @@
+"""Thin Python launchers of the tcgen05 convolution kernels.
+
+All tensors here are *voxel-major* views: activations ``[N, D, H, W, C]`` bf16
+contiguous (the memory of an NCDHW ``channels_last_3d`` tensor), packed
+weights bf16, weight gradients fp32 in the parameter's own layout. Autograd,
+module parameters and the CPU path live in :mod:`scaffold_b200.ops.conv3d`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+
+
+def _pad_to(v: int, m: int) -> int:
+    return (v + m - 1) // m * m
+
+
+def pad_channels(c: int) -> int:
+    """Channel counts the kernels accept: multiples of 16."""
+    return _pad_to(c, 16)
+
+
+# ---------------------------------------------------------------------------
+# weight packing (bf16 operand copies; the fp32 parameter stays the master)
+# ---------------------------------------------------------------------------
+def pack_weight_fwd(w: torch.Tensor) -> torch.Tensor:
+    """[Cout, Cin, k, k, k] -> bf16 [taps, cout_pad, cin_pad] (taps = kd,kh,kw row-major)."""
+    co, ci = w.shape[:2]
+    taps = w.shape[2] * w.shape[3] * w.shape[4]
+    out = torch.zeros(taps, pad_channels(co), pad_channels(ci), dtype=torch.bfloat16, device=w.device)
+    out[:, :co, :ci] = w.reshape(co, ci, taps).permute(2, 0, 1)
+    return out
+
+
+def pack_weight_dgrad(w: torch.Tensor) -> torch.Tensor:
+    """Backward-data operand: bf16 [taps, cin_pad, cout_pad], taps flipped."""
+    co, ci = w.shape[:2]
+    taps = w.shape[2] * w.shape[3] * w.shape[4]
+    out = torch.zeros(taps, pad_channels(ci), pad_channels(co), dtype=torch.bfloat16, device=w.device)
+    out[:, :ci, :co] = w.reshape(co, ci, taps).flip(2).permute(2, 1, 0)
+    return out
+
+
+def pack_weight_convT_fwd(w: torch.Tensor) -> torch.Tensor:
+    """[Cin, Cout, 2,2,2] -> bf16 [8*Cout, Cin] (row = tap*Cout + co)."""
+    ci, co = w.shape[:2]
+    return w.reshape(ci, co, 8).permute(2, 1, 0).reshape(8 * co, ci).to(torch.bfloat16).contiguous()
+
+
+def pack_weight_convT_dgrad(w: torch.Tensor) -> torch.Tensor:
+    """[Cin, Cout, 2,2,2] -> bf16 [4, cin_pad, 2*Cout] (outer = kd*2+kh, col = kw*Cout + co)."""
+    ci, co = w.shape[:2]
+    out = torch.zeros(4, pad_channels(ci), 2 * co, dtype=torch.bfloat16, device=w.device)
+    # w[ci, co, kd, kh, kw] -> [kd, kh, ci, kw, co]
+    out[:, :ci] = w.permute(2, 3, 0, 4, 1).reshape(4, ci, 2 * co)
+    return out
+
+
+# ---------------------------------------------------------------------------
+# launchers
+# ---------------------------------------------------------------------------
+def _chk_act(t: torch.Tensor) -> None:
+    if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.dim() != 5:
+        raise ValueError(f"expected a contiguous bf16 [N,D,H,W,C] tensor, got {t.dtype} {tuple(t.shape)} "
+                         f"contiguous={t.is_contiguous()}")
+
+
+def conv_same(srcs: Sequence[torch.Tensor], wpack: torch.Tensor, ksize: int,
+              dst_channels: Sequence[int], bias: Optional[torch.Tensor] = None,
+              force_plain: bool = False, out: Optional[Sequence[torch.Tensor]] = None):
+    """Stride-1 'same' convolution of the channel concatenation of ``srcs``.
+
+    Returns a list of outputs, one per entry of ``dst_channels`` (the output
+    channels are split in that order).
+    """
+    for s in srcs:
+        _chk_act(s)
+    n, d, h, w = srcs[0].shape[:4]
+    a = _lib.SbConvArgs()
+    for i in range(2):
+        if i < len(srcs):
+            a.src[i] = srcs[i].data_ptr()
+            a.src_c[i] = srcs[i].shape[4]
+            a.src_ld[i] = srcs[i].shape[4]
+        else:
+            a.src[i] = None
+            a.src_c[i] = 0
+            a.src_ld[i] = 0
+    a.N, a.D, a.H, a.W = n, d, h, w
+    a.ksize = ksize
+    a.wpack = wpack.data_ptr()
+    a.cout_pad = wpack.shape[1]
+    if wpack.shape[2] != sum(s.shape[4] for s in srcs):
+        raise ValueError(f"packed weight K {wpack.shape[2]} != source channels {[s.shape[4] for s in srcs]}")
+    outs = list(out) if out is not None else [
+        torch.empty((n, d, h, w, c), dtype=torch.bfloat16, device=srcs[0].device) for c in dst_channels]
+    for i in range(2):
+        if i < len(outs):
+            a.dst[i] = outs[i].data_ptr()
+            a.dst_c[i] = outs[i].shape[4]
+            a.dst_ld[i] = outs[i].shape[4]
+        else:
+            a.dst[i] = None
+            a.dst_c[i] = 0
+            a.dst_ld[i] = 0
+    a.bias = _lib.ptr(bias)
+    a.status = _lib.status_tensor(srcs[0].device).data_ptr()
+    a.force_plain = 1 if force_plain else 0
+    _lib.check(_lib.lib().sb_conv_fwd(C.byref(a), _lib.stream_ptr()), "sb_conv_fwd")
+    return outs
+
+
+def convT_fwd(x: torch.Tensor, wpack: torch.Tensor, cout: int, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    _chk_act(x)
+    n, d, h, w, cin = x.shape
+    y = torch.empty((n, 2 * d, 2 * h, 2 * w, cout), dtype=torch.bfloat16, device=x.device)
+    a = _lib.SbConvTArgs()
+    a.src, a.src_ld = x.data_ptr(), cin
+    a.N, a.D, a.H, a.W = n, d, h, w
+    a.cin, a.cout = cin, cout
+    a.wpack, a.wrows = wpack.data_ptr(), wpack.shape[0]
+    a.dst, a.dst_ld = y.data_ptr(), cout
+    a.bias = _lib.ptr(bias)
+    a.status = _lib.status_tensor(x.device).data_ptr()
+    _lib.check(_lib.lib().sb_convT_fwd(C.byref(a), _lib.stream_ptr()), "sb_convT_fwd")
+    return y
+
+
+def convT_dgrad(gy: torch.Tensor, wpack: torch.Tensor, cin_store: int) -> torch.Tensor:
+    """gy [N,2D,2H,2W,Cout] -> gx [N,D,H,W,cin_store]."""
+    _chk_act(gy)
+    n, d2, h2, w2, cout = gy.shape
+    d, h, w = d2 // 2, h2 // 2, w2 // 2
+    gx = torch.empty((n, d, h, w, cin_store), dtype=torch.bfloat16, device=gy.device)
+    a = _lib.SbConvTArgs()
+    a.src, a.src_ld = gy.data_ptr(), cout
+    a.N, a.D, a.H, a.W = n, d, h, w
+    a.cin, a.cout = cin_store, cout
+    a.wpack, a.wrows = wpack.data_ptr(), wpack.shape[1]
+    a.dst, a.dst_ld = gx.data_ptr(), cin_store
+    a.bias = None
+    a.status = _lib.status_tensor(gy.device).data_ptr()
+    _lib.check(_lib.lib().sb_convT_dgrad(C.byref(a), _lib.stream_ptr()), "sb_convT_dgrad")
+    return gx
+
+
+_workspaces: dict = {}
+
+
+def _workspace(device, elems: int) -> torch.Tensor:
+    key = torch.device(device).index or 0
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < elems:
+        ws = torch.empty(max(elems, 1 << 22), dtype=torch.float32, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def conv_wgrad(gy: torch.Tensor, xs: Sequence[torch.Tensor], ksize: int, dw: torch.Tensor,
+               accumulate: bool = False, splits: int = 0) -> torch.Tensor:
+    """Weight gradient into ``dw`` (fp32, parameter layout).
+
+    ksize 1/3: ``dw`` is [Cout, Cin, k,k,k]; ``gy`` and ``xs`` share the voxel grid.
+    ksize 2:   k2s2 transposed conv, ``dw`` is [Cin, Cout, 2,2,2]; ``gy`` is on the fine grid.
+    """
+    _chk_act(gy)
+    for x in xs:
+        _chk_act(x)
+    n, d, h, w = xs[0].shape[:4]
+    a = _lib.SbWgradArgs()
+    a.gy, a.gy_c, a.gy_ld = gy.data_ptr(), gy.shape[4], gy.shape[4]
+    for i in range(2):
+        if i < len(xs):
+            a.x[i], a.x_c[i], a.x_ld[i] = xs[i].data_ptr(), xs[i].shape[4], xs[i].shape[4]
+        else:
+            a.x[i], a.x_c[i], a.x_ld[i] = None, 0, 0
+    a.N, a.D, a.H, a.W = n, d, h, w
+    a.ksize = ksize
+    a.splits = splits
+    a.accumulate = 1 if accumulate else 0
+    if not (dw.dtype == torch.float32 and dw.is_contiguous()):
+        raise ValueError("dw must be contiguous fp32")
+    if ksize == 2:
+        a.dw_cin, a.dw_cout = dw.shape[0], dw.shape[1]
+    else:
+        a.dw_cout, a.dw_cin = dw.shape[0], dw.shape[1]
+    L = _lib.lib()
+    need = L.sb_conv_wgrad_workspace(C.byref(a))
+    if need < 0:
+        raise _lib.NativeError(f"sb_conv_wgrad: unsupported shape gy={tuple(gy.shape)} xs={[tuple(x.shape) for x in xs]}")
+    ws = _workspace(gy.device, need)
+    a.workspace, a.workspace_elems = ws.data_ptr(), ws.numel()
+    a.dw = dw.data_ptr()
+    a.status = _lib.status_tensor(gy.device).data_ptr()
+    _lib.check(L.sb_conv_wgrad(C.byref(a), _lib.stream_ptr()), "sb_conv_wgrad")
+    return dw
