@@ -38,7 +38,8 @@ struct IgemmParams {
   CUtensorMap mapA[8];
   CUtensorMap mapB;
   int TH, TW, TD, TN;
-  int KWS, n_outer, BK, BN;
+  int KWS, KHS, n_outer, BK, BN;
+  int base_off_mode;
   int stages, stage_bytes, a_bytes, b_bytes, tx_bytes;  // a_bytes: offset of B inside a stage
   int N, D, H, W;  // output voxel grid (== the grid the tile bricks walk)
   int tiles_h, tiles_w, tiles_d, tiles_n, tiles_co, num_tiles;
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(192, 1) igemm_kernel(const __grid_constant__ I
             const int c = (second ? cb - p.cblks0 : cb) * p.BK;
             tma_load_5d(sa, &p.mapA[mi], &full_bar[s], c, h0 + p.tap_dh[o], w0 + p.tap_dw[o],
                         d0 + p.tap_dd[o], n0);
-            tma_load_3d(sbm, &p.mapB, &full_bar[s], cb * p.BK, co0, o * p.KWS);
+            tma_load_3d(sbm, &p.mapB, &full_bar[s], cb * p.BK, co0, o * p.KWS * p.KHS);
           }
         }
       }
@@ -134,8 +135,8 @@ __global__ void __launch_bounds__(192, 1) igemm_kernel(const __grid_constant__ I
     if (lane == 0) {
       const uint32_t idesc = make_idesc_bf16(128, p.BN, 0, 0);
       const uint32_t swz = swizzle_code_for(rowb);
-      const uint32_t sbo = 8u * rowb;
-      const uint32_t a_shift = (uint32_t)p.TH * rowb;  // one w step == TH rows
+      const int rh = p.TH + p.KHS - 1;             // rows per w column of the A box
+      const uint32_t sbo = (uint32_t)rh * rowb;    // 8-row groups are one w step apart
       const uint32_t b_shift = (uint32_t)p.BN * rowb;
       uint32_t it = 0, tcount = 0;
       bool ok = true;
@@ -152,11 +153,16 @@ __global__ void __launch_bounds__(192, 1) igemm_kernel(const __grid_constant__ I
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + (size_t)s * p.stage_bytes);
           const uint32_t sbm = sa + p.a_bytes;
-          for (int kw = 0; kw < p.KWS; ++kw) {
-            for (int k = 0; k < p.BK / 16; ++k) {
-              const uint64_t da = make_smem_desc(sa + kw * a_shift + k * 32u, 16u, sbo, swz);
-              const uint64_t db = make_smem_desc(sbm + kw * b_shift + k * 32u, 16u, sbo, swz);
-              tc_mma_bf16(acc, da, db, idesc, (ki | kw | k) != 0 ? 1u : 0u);
+          for (int kh = 0; kh < p.KHS; ++kh) {
+            for (int kw = 0; kw < p.KWS; ++kw) {
+              const uint32_t a0 = sa + (uint32_t)(kw * rh + kh) * rowb;
+              const uint32_t b0 = sbm + (uint32_t)(kh * p.KWS + kw) * b_shift;
+              for (int k = 0; k < p.BK / 16; ++k) {
+                uint64_t da = make_smem_desc(a0 + k * 32u, 16u, sbo, swz);
+                if (p.base_off_mode) da |= (uint64_t)((a0 >> 7) & 7u) << 49;
+                const uint64_t db = make_smem_desc(b0 + k * 32u, 16u, 8u * rowb, swz);
+                tc_mma_bf16(acc, da, db, idesc, (ki | kh | kw | k) != 0 ? 1u : 0u);
+              }
             }
           }
           tc_commit(&empty_bar[s]);
@@ -343,6 +349,7 @@ static int device_setup() {
 
 // Choose the voxel brick and finish the geometry common to all plans.
 static void choose_brick(IgemmParams& p, bool shift) {
+  p.KHS = 1;
   if (shift) {
     p.TH = 8; p.TW = 16; p.TD = 1; p.TN = 1; p.KWS = 3;
   } else {
@@ -364,11 +371,11 @@ static void choose_brick(IgemmParams& p, bool shift) {
 
 static int finish_and_launch(IgemmParams& p, int cout_rows, cudaStream_t stream) {
   const int rowb = p.BK * 2;
-  const int rows_a = p.TH * (p.TW + p.KWS - 1) * p.TD * p.TN;
+  const int rows_a = (p.TH + p.KHS - 1) * (p.TW + p.KWS - 1) * p.TD * p.TN;
   // the MMA always reads 128 rows starting at an offset of up to (KWS-1)*TH rows
   const int rows_alloc = rows_a > 128 + (p.KWS - 1) * p.TH ? rows_a : 128 + (p.KWS - 1) * p.TH;
   p.a_bytes = ((rows_alloc * rowb + 1023) / 1024) * 1024;
-  p.b_bytes = p.KWS * p.BN * rowb;
+  p.b_bytes = p.KWS * p.KHS * p.BN * rowb;
   p.stage_bytes = ((p.a_bytes + p.b_bytes + 1023) / 1024) * 1024;
   int st = (g_smem_limit - 1024) / p.stage_bytes;
   if (st > MAX_STAGES) st = MAX_STAGES;
@@ -406,14 +413,19 @@ extern "C" int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream) {
   if (p.BN % 16 != 0 || a->cout_pad % p.BN != 0) return SB_ERR_SHAPE;
   if (a->ksize != 1 && a->ksize != 3) return SB_ERR_SHAPE;
   p.N = a->N; p.D = a->D; p.H = a->H; p.W = a->W;
-  const bool shift = a->ksize == 3 && a->W >= 16 && a->H >= 8 && !a->force_plain;
+  const bool can_shift = a->ksize == 3 && a->W >= 16 && a->H >= 8;
+  const bool shift = can_shift && a->force_plain != 1;
   choose_brick(p, shift);
+  if (shift && a->force_plain >= 2) {
+    p.KHS = 3;
+    p.base_off_mode = a->force_plain == 3 ? 1 : 0;
+  }
   const int taps = a->ksize * a->ksize * a->ksize;
-  p.n_outer = taps / p.KWS;
+  p.n_outer = taps / (p.KWS * p.KHS);
   p.maps_per_tap = nsrc;
   const int half = a->ksize / 2;
   for (int o = 0; o < p.n_outer; ++o) {
-    const int t0 = o * p.KWS;  // taps ordered (kd, kh, kw), kw fastest
+    const int t0 = o * p.KWS * p.KHS;  // taps ordered (kd, kh, kw), kw fastest
     const int kd = t0 / (a->ksize * a->ksize), kh = (t0 / a->ksize) % a->ksize, kw = t0 % a->ksize;
     p.tap_map[o] = 0;
     p.tap_dd[o] = (signed char)(kd - half);
@@ -427,7 +439,7 @@ extern "C" int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream) {
     const long long C = a->src_ld[s];
     long long dims[5] = {a->src_c[s], a->H, a->W, a->D, a->N};
     long long str[5] = {1, (long long)a->W * C, C, (long long)a->H * a->W * C, (long long)a->D * a->H * a->W * C};
-    int box[5] = {bk, p.TH, p.TW + p.KWS - 1, p.TD, p.TN};
+    int box[5] = {bk, p.TH + p.KHS - 1, p.TW + p.KWS - 1, p.TD, p.TN};
     rc = make_map_bf16(&p.mapA[s], a->src[s], 5, dims, str, box, rowb);
     if (rc) return rc;
   }
@@ -435,7 +447,7 @@ extern "C" int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream) {
   {
     long long dims[3] = {cin_tot, a->cout_pad, taps};
     long long str[3] = {1, cin_tot, (long long)a->cout_pad * cin_tot};
-    int box[3] = {bk, p.BN, p.KWS};
+    int box[3] = {bk, p.BN, p.KWS * p.KHS};
     rc = make_map_bf16(&p.mapB, a->wpack, 3, dims, str, box, rowb);
     if (rc) return rc;
   }

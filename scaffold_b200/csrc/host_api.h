@@ -73,6 +73,36 @@ typedef struct {
   int splits;         // 0: choose
 } SbWgradArgs;
 
+// GroupNorm (+ReLU), channels-last bf16. `parts` lists the partial-statistics
+// buffers to merge: this rank's own first, then the spatial peers' (device
+// pointers valid on this GPU). S is the local voxel count per sample, S_total
+// the voxel count per sample over all shards.
+typedef struct {
+  const void* x;
+  const void* dy;
+  void* y;
+  const float* w;
+  const float* b;
+  float* mean;
+  float* rstd;
+  float* part;
+  const float* parts[8];
+  int n_parts;
+  float* dw;
+  float* db;
+  int N, C, G;
+  long long S, S_total;
+  int nsplit;
+  float eps;
+  int relu;
+} SbGnArgs;
+
+int sb_gn_nsplit(int N, long long S, int C);
+int sb_gn_stats(const SbGnArgs* a, cudaStream_t stream);
+int sb_gn_apply(const SbGnArgs* a, cudaStream_t stream);
+int sb_gn_bwd_partial(const SbGnArgs* a, cudaStream_t stream);
+int sb_gn_bwd_dx(const SbGnArgs* a, cudaStream_t stream);
+
 int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream);
 int sb_convT_fwd(const SbConvTArgs* a, cudaStream_t stream);
 int sb_convT_dgrad(const SbConvTArgs* a, cudaStream_t stream);

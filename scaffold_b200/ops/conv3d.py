@@ -1,0 +1,211 @@
+"""Convolution modules: stock parameter names, sm_100a kernels on CUDA, ATen on CPU.
+
+``Conv3d`` / ``ConvTranspose3d`` subclass the ``torch.nn`` modules, so their
+state dicts are interchangeable with the stock ones (weights ``(Cout,Cin,k,k,k)``
+and ``(Cin,Cout,2,2,2)``, no buffers); packed bf16 operand copies are caches
+outside the state dict, refreshed when the parameter's version changes.
+
+On CUDA with bf16 activations (or under autocast) the forward, backward-data
+and weight-gradient all run on the tcgen05 kernels of ``csrc/conv_igemm.cu`` and
+``csrc/conv_wgrad.cu``; there is no library fallback on that path. A CPU tensor
+(the gloo plumbing runs) takes ATen.
+
+``Conv3d.forward`` accepts one tensor or a sequence of tensors that are read as
+their channel concatenation: the U-Net skip concat is never materialised on the
+CUDA path (role of ``_skip_concat``, ScaFFold/unet/unet_parts.py:76-120, and of
+``FastConv3d``/``FastConvTranspose3d``, ScaFFold/unet/conv3d.py:1235-1904).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Union
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import conv_kernels as ck
+from .layout import from_vm, to_vm, use_cuda_kernels, weights_epoch
+
+
+class _PackCache:
+    """bf16 operand copies of one parameter, keyed by (tensor identity, version)."""
+
+    def __init__(self):
+        self._key = None
+        self._vals = {}
+
+    def get(self, w: torch.Tensor, name: str, fn):
+        key = (w.data_ptr(), w._version, w.device, weights_epoch())
+        if key != self._key:
+            self._key = key
+            self._vals = {}
+        v = self._vals.get(name)
+        if v is None:
+            with torch.no_grad():
+                v = fn(w.detach().float())
+            self._vals[name] = v
+        return v
+
+
+def _pad_in_channels(w: torch.Tensor, src_channels: Sequence[int], real: Sequence[int]) -> torch.Tensor:
+    """Insert zero input-channel columns so the weight matches channel-padded sources."""
+    if list(src_channels) == list(real):
+        return w
+    parts, o = [], 0
+    for sc, rc in zip(src_channels, real):
+        blk = w[:, o:o + rc]
+        if sc > rc:
+            blk = F.pad(blk, (0, 0, 0, 0, 0, 0, 0, sc - rc))
+        parts.append(blk)
+        o += rc
+    return torch.cat(parts, 1)
+
+
+class _ConvSameFn(torch.autograd.Function):
+    """k in {1,3} stride-1 'same' conv over voxel-major bf16 sources."""
+
+    @staticmethod
+    def forward(ctx, weight, bias, mod, n_src, *xs):
+        ks = weight.shape[2]
+        src_c = [x.shape[4] for x in xs]
+        real_c = mod._real_in_channels(src_c)
+        wf = mod._cache.get(weight, f"fwd{src_c}", lambda w: ck.pack_weight_fwd(_pad_in_channels(w, src_c, real_c)))
+        cout_pad = wf.shape[1]
+        bpad = None
+        if bias is not None:
+            bpad = mod._cache_b.get(bias, "b", lambda b: F.pad(b, (0, cout_pad - b.shape[0])).contiguous())
+        (y,) = ck.conv_same(list(xs), wf, ks, [cout_pad], bias=bpad)
+        ctx.mod = mod
+        ctx.src_c, ctx.real_c = src_c, real_c
+        ctx.has_bias = bias is not None
+        ctx.save_for_backward(weight, *xs)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        weight, *xs = ctx.saved_tensors
+        mod = ctx.mod
+        ks = weight.shape[2]
+        gy = gy.contiguous()
+        src_c, real_c = ctx.src_c, ctx.real_c
+        gxs: List[Optional[torch.Tensor]] = [None] * len(xs)
+        need_gx = [ctx.needs_input_grad[4 + i] for i in range(len(xs))]
+        if any(need_gx):
+            def pack(w):
+                # pack_weight_dgrad pads Cout to a multiple of 16, which is gy's channel count
+                return ck.pack_weight_dgrad(_pad_in_channels(w, src_c, real_c))
+            wd = mod._cache.get(weight, f"dgrad{src_c}", pack)
+            outs = ck.conv_same([gy], wd, ks, src_c)
+            for i, o in enumerate(outs):
+                if need_gx[i]:
+                    gxs[i] = o
+        gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gw = torch.empty_like(weight, dtype=torch.float32)
+            if list(src_c) == list(real_c):
+                ck.conv_wgrad(gy, list(xs), ks, gw)
+            else:
+                # channel-padded sources (the 3-channel stem): gradient over padded Cin, then slice
+                gwp = torch.empty((weight.shape[0], sum(src_c), ks, ks, ks), dtype=torch.float32, device=gy.device)
+                ck.conv_wgrad(gy, list(xs), ks, gwp)
+                parts, o = [], 0
+                for sc, rc in zip(src_c, real_c):
+                    parts.append(gwp[:, o:o + rc])
+                    o += sc
+                gw = torch.cat(parts, 1).contiguous()
+        if ctx.has_bias and ctx.needs_input_grad[1]:
+            gb = gy.reshape(-1, gy.shape[4]).sum(0, dtype=torch.float32)[: weight.shape[0]]
+        return (gw, gb, None, None, *gxs)
+
+
+class Conv3d(nn.Conv3d):
+    """3-D convolution; drop-in for ``nn.Conv3d`` (k=1 or k=3 'same', stride 1 on the CUDA path)."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self._cache = _PackCache()
+        self._cache_b = _PackCache()
+
+    def _real_in_channels(self, src_c: Sequence[int]) -> List[int]:
+        """Real (unpadded) channel count of each source; only a single source may be padded."""
+        if len(src_c) == 1:
+            return [self.in_channels]
+        if sum(src_c) != self.in_channels:
+            raise ValueError(f"sources {list(src_c)} do not add up to in_channels={self.in_channels}")
+        return list(src_c)
+
+    def _kernel_ok(self) -> bool:
+        k = self.kernel_size
+        return (k[0] == k[1] == k[2] and k[0] in (1, 3) and self.stride == (1, 1, 1) and self.dilation == (1, 1, 1)
+                and self.groups == 1 and self.padding == (k[0] // 2,) * 3 and self.padding_mode == "zeros")
+
+    def forward(self, x: Union[torch.Tensor, Sequence[torch.Tensor]]) -> torch.Tensor:
+        xs = [x] if isinstance(x, torch.Tensor) else list(x)
+        if use_cuda_kernels(xs[0]):
+            if not self._kernel_ok():
+                raise NotImplementedError(
+                    f"sm_100a conv kernels cover k in (1,3), stride 1, 'same' zero padding; got {self}")
+            vms = [to_vm(t, pad16=True) for t in xs]
+            y = _ConvSameFn.apply(self.weight, self.bias, self, len(vms), *vms)
+            out = from_vm(y)
+            return out if y.shape[4] == self.out_channels else out[:, : self.out_channels]
+        xin = xs[0] if len(xs) == 1 else torch.cat([t.to(xs[0].dtype) for t in xs], dim=1)
+        return super().forward(xin)
+
+    def forward_padded(self, x) -> torch.Tensor:
+        """CUDA path only: voxel-major output with the channel axis padded to a multiple of 16."""
+        xs = [x] if isinstance(x, torch.Tensor) else list(x)
+        vms = [to_vm(t, pad16=True) for t in xs]
+        return _ConvSameFn.apply(self.weight, self.bias, self, len(vms), *vms)
+
+
+class _ConvTFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, weight, bias, mod, x):
+        cout = weight.shape[1]
+        wf = mod._cache.get(weight, "fwd", ck.pack_weight_convT_fwd)
+        b32 = None
+        if bias is not None:
+            b32 = mod._cache_b.get(bias, "b", lambda b: b.contiguous())
+        y = ck.convT_fwd(x, wf, cout, b32)
+        ctx.mod = mod
+        ctx.has_bias = bias is not None
+        ctx.save_for_backward(weight, x)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        weight, x = ctx.saved_tensors
+        mod = ctx.mod
+        gy = gy.contiguous()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[3]:
+            wd = mod._cache.get(weight, "dgrad", ck.pack_weight_convT_dgrad)
+            gx = ck.convT_dgrad(gy, wd, x.shape[4])
+        if ctx.needs_input_grad[0]:
+            gw = torch.empty_like(weight, dtype=torch.float32)
+            ck.conv_wgrad(gy, [x], 2, gw)
+        if ctx.has_bias and ctx.needs_input_grad[1]:
+            gb = gy.reshape(-1, gy.shape[4]).sum(0, dtype=torch.float32)
+        return gw, gb, None, gx
+
+
+class ConvTranspose3d(nn.ConvTranspose3d):
+    """k=2, s=2 transposed convolution (the U-Net upsampler); drop-in for ``nn.ConvTranspose3d``."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self._cache = _PackCache()
+        self._cache_b = _PackCache()
+
+    def _kernel_ok(self) -> bool:
+        return (self.kernel_size == (2, 2, 2) and self.stride == (2, 2, 2) and self.padding == (0, 0, 0)
+                and self.output_padding == (0, 0, 0) and self.groups == 1 and self.dilation == (1, 1, 1)
+                and self.in_channels % 16 == 0 and self.out_channels % 8 == 0)
+
+    def forward(self, x: torch.Tensor, output_size=None) -> torch.Tensor:
+        if use_cuda_kernels(x):
+            if not self._kernel_ok() or output_size is not None:
+                raise NotImplementedError(f"sm_100a transposed-conv kernel covers k=2, s=2, no padding; got {self}")
+            return from_vm(_ConvTFn.apply(self.weight, self.bias, self, to_vm(x)))
+        return super().forward(x, output_size)

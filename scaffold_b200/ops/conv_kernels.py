@@ -109,7 +109,7 @@ def conv_same(srcs: Sequence[torch.Tensor], wpack: torch.Tensor, ksize: int,
             a.dst_ld[i] = 0
     a.bias = _lib.ptr(bias)
     a.status = _lib.status_tensor(srcs[0].device).data_ptr()
-    a.force_plain = 1 if force_plain else 0
+    a.force_plain = int(force_plain)
     _lib.check(_lib.lib().sb_conv_fwd(C.byref(a), _lib.stream_ptr()), "sb_conv_fwd")
     return outs
 

@@ -1,0 +1,128 @@
+"""Launchers of the channels-last GroupNorm(+ReLU) kernels (``csrc/group_norm.cu``).
+
+Tensors are voxel-major ``[N, D, H, W, C]`` bf16; affine parameters and
+statistics are fp32. ``peer_parts`` lets a spatially sharded run merge the
+neighbours' partial statistics (device pointers into their memory) so the
+result equals the unsharded normalisation.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+
+_lib.register("sb_gn_nsplit", [C.c_int, C.c_longlong, C.c_int], C.c_int)
+
+
+class SbGnArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("dy", C.c_void_p), ("y", C.c_void_p),
+        ("w", C.c_void_p), ("b", C.c_void_p),
+        ("mean", C.c_void_p), ("rstd", C.c_void_p),
+        ("part", C.c_void_p),
+        ("parts", C.c_void_p * 8),
+        ("n_parts", C.c_int),
+        ("dw", C.c_void_p), ("db", C.c_void_p),
+        ("N", C.c_int), ("C", C.c_int), ("G", C.c_int),
+        ("S", C.c_longlong), ("S_total", C.c_longlong),
+        ("nsplit", C.c_int),
+        ("eps", C.c_float),
+        ("relu", C.c_int),
+    ]
+
+
+for _n in ("sb_gn_stats", "sb_gn_apply", "sb_gn_bwd_partial", "sb_gn_bwd_dx"):
+    _lib.register(_n, [C.POINTER(SbGnArgs), C.c_void_p], C.c_int)
+
+
+def _base(x: torch.Tensor, w, b, groups: int, eps: float, relu: bool, shards: int) -> SbGnArgs:
+    n, d, h, wd, c = x.shape
+    a = SbGnArgs()
+    a.x = x.data_ptr()
+    a.w, a.b = w.data_ptr(), b.data_ptr()
+    a.N, a.C, a.G = n, c, groups
+    a.S = d * h * wd
+    a.S_total = a.S * shards
+    a.nsplit = _lib.lib().sb_gn_nsplit(n, a.S, c)
+    a.eps = eps
+    a.relu = 1 if relu else 0
+    return a
+
+
+def partial_numel_fwd(x: torch.Tensor, groups: int) -> int:
+    n, d, h, w, c = x.shape
+    return n * _lib.lib().sb_gn_nsplit(n, d * h * w, c) * groups * 3
+
+
+def partial_numel_bwd(x: torch.Tensor) -> int:
+    n, d, h, w, c = x.shape
+    return n * _lib.lib().sb_gn_nsplit(n, d * h * w, c) * c * 2
+
+
+def gn_stats(x, w, b, groups, eps, relu, part: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Pass 1: this rank's partial (count, mean, M2) per (n, split, group)."""
+    a = _base(x, w, b, groups, eps, relu, 1)
+    if part is None:
+        part = torch.empty(partial_numel_fwd(x, groups), dtype=torch.float32, device=x.device)
+    a.part = part.data_ptr()
+    a.n_parts = 1
+    a.parts[0] = part.data_ptr()
+    _lib.check(_lib.lib().sb_gn_stats(C.byref(a), _lib.stream_ptr()), "sb_gn_stats")
+    return part
+
+
+def gn_apply(x, w, b, groups, eps, relu, parts: Sequence[int], shards: int = 1):
+    """Pass 2: merge ``parts`` (device pointers, own first) and normalise."""
+    a = _base(x, w, b, groups, eps, relu, shards)
+    n = x.shape[0]
+    y = torch.empty_like(x)
+    mean = torch.empty((n, groups), dtype=torch.float32, device=x.device)
+    rstd = torch.empty((n, groups), dtype=torch.float32, device=x.device)
+    a.y, a.mean, a.rstd = y.data_ptr(), mean.data_ptr(), rstd.data_ptr()
+    a.n_parts = len(parts)
+    for i, p in enumerate(parts):
+        a.parts[i] = p
+    _lib.check(_lib.lib().sb_gn_apply(C.byref(a), _lib.stream_ptr()), "sb_gn_apply")
+    return y, mean, rstd
+
+
+def gn_forward(x, w, b, groups: int, eps: float = 1e-5, relu: bool = True):
+    part = gn_stats(x, w, b, groups, eps, relu)
+    return gn_apply(x, w, b, groups, eps, relu, [part.data_ptr()])
+
+
+def gn_bwd_partial(dy, x, w, b, mean, rstd, groups, eps, relu, part: Optional[torch.Tensor] = None):
+    a = _base(x, w, b, groups, eps, relu, 1)
+    a.dy = dy.data_ptr()
+    a.mean, a.rstd = mean.data_ptr(), rstd.data_ptr()
+    if part is None:
+        part = torch.empty(partial_numel_bwd(x), dtype=torch.float32, device=x.device)
+    a.part = part.data_ptr()
+    a.n_parts = 1
+    a.parts[0] = part.data_ptr()
+    _lib.check(_lib.lib().sb_gn_bwd_partial(C.byref(a), _lib.stream_ptr()), "sb_gn_bwd_partial")
+    return part
+
+
+def gn_bwd_dx(dy, x, w, b, mean, rstd, groups, eps, relu, parts: Sequence[int], shards: int = 1):
+    a = _base(x, w, b, groups, eps, relu, shards)
+    a.dy = dy.data_ptr()
+    a.mean, a.rstd = mean.data_ptr(), rstd.data_ptr()
+    dx = torch.empty_like(x)
+    c = x.shape[4]
+    dw = torch.empty(c, dtype=torch.float32, device=x.device)
+    db = torch.empty(c, dtype=torch.float32, device=x.device)
+    a.y, a.dw, a.db = dx.data_ptr(), dw.data_ptr(), db.data_ptr()
+    a.n_parts = len(parts)
+    for i, p in enumerate(parts):
+        a.parts[i] = p
+    _lib.check(_lib.lib().sb_gn_bwd_dx(C.byref(a), _lib.stream_ptr()), "sb_gn_bwd_dx")
+    return dx, dw, db
+
+
+def gn_backward(dy, x, w, b, mean, rstd, groups: int, eps: float = 1e-5, relu: bool = True):
+    part = gn_bwd_partial(dy, x, w, b, mean, rstd, groups, eps, relu)
+    return gn_bwd_dx(dy, x, w, b, mean, rstd, groups, eps, relu, [part.data_ptr()])

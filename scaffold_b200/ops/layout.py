@@ -1,0 +1,51 @@
+"""Activation layout helpers.
+
+Modules exchange ordinary NCDHW-shaped tensors whose memory is channels-last
+(``torch.channels_last_3d``); the kernels see the same memory as a contiguous
+voxel-major ``[N, D, H, W, C]`` tensor. Both conversions are views when the
+memory format already matches.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+AMP_DTYPE = torch.bfloat16
+
+
+def use_cuda_kernels(x: torch.Tensor) -> bool:
+    """True when the sm_100a kernel path applies: CUDA tensor, bf16 or autocast-to-bf16."""
+    if not x.is_cuda:
+        return False
+    if x.dtype == torch.bfloat16:
+        return True
+    return torch.is_autocast_enabled() and torch.get_autocast_gpu_dtype() == torch.bfloat16
+
+
+def to_vm(x: torch.Tensor, pad16: bool = False) -> torch.Tensor:
+    """NCDHW-shaped tensor -> contiguous voxel-major bf16 ``[N, D, H, W, C]``."""
+    v = x.permute(0, 2, 3, 4, 1)
+    if v.dtype != torch.bfloat16:
+        v = v.to(torch.bfloat16)
+    c = v.shape[4]
+    if pad16 and c % 16 != 0:
+        v = F.pad(v, (0, 16 - c % 16))
+    return v.contiguous()
+
+
+def from_vm(y: torch.Tensor) -> torch.Tensor:
+    """Voxel-major ``[N, D, H, W, C]`` -> NCDHW-shaped view (channels-last memory)."""
+    return y.permute(0, 4, 1, 2, 3)
+
+
+# Parameters updated through raw pointers (the fused optimizer) do not bump the
+# tensors' version counters; packed operand caches also key on this epoch.
+_weights_epoch = [0]
+
+
+def bump_weights_epoch() -> None:
+    _weights_epoch[0] += 1
+
+
+def weights_epoch() -> int:
+    return _weights_epoch[0]
