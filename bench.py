@@ -1,0 +1,240 @@
+#!/usr/bin/env python
+"""Headline benchmark: 3-D U-Net training throughput in voxels/s.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+One rank per GPU (under ``torch.distributed.run`` for N > 1), synthetic
+fractal-shaped data (random volumes/labels of the configured shape), random
+initial weights, bf16 autocast, the complete training step (forward, loss,
+backward, gradient reduction, clip + Adam). Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--scale", type=int, default=7, help="problem_scale (volume edge 2**scale)")
+    ap.add_argument("--batch", type=int, default=2, help="samples per data-parallel replica")
+    ap.add_argument("--n-categories", type=int, default=8)
+    ap.add_argument("--base-width", type=int, default=64)
+    ap.add_argument("--bottleneck-dim", type=int, default=3)
+    ap.add_argument("--dc-num-shards", type=int, nargs=3, default=[1, 1, 1])
+    ap.add_argument("--grad-allreduce", default="fused", choices=["fused", "nccl"])
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def baseline_value():
+    """BASELINE.md publishes no end-to-end throughput, so there is nothing to divide by."""
+    return None
+
+
+def run_reference(args):
+    from baseline.reference_arm import run as run_ref
+    return run_ref(args)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        try:
+            out = run_reference(args)
+        except Exception as exc:  # the reference arm must never fail the driver
+            out = {"impl": "reference", "unavailable": f"{type(exc).__name__}: {str(exc).splitlines()[0][:200]}"}
+        if out is not None:
+            print(json.dumps(out), flush=True)
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    from scaffold_b200.models.unet import UNet
+    from scaffold_b200.ops import _lib
+    from scaffold_b200.ops.optim import FusedClipAdam
+    from scaffold_b200.parallel.layout import ParallelLayout
+    from scaffold_b200.train.engine import TrainEngine
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit(f"--gpus {args.gpus} needs a torch.distributed.run launch with {args.gpus} ranks")
+        args.gpus = world
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    layout = ParallelLayout(args.dc_num_shards, (2, 3, 4), world, rank)
+
+    torch.manual_seed(42)
+    n_classes = args.n_categories + 1
+    layers = args.scale - args.bottleneck_dim
+    model = UNet(3, n_classes, layers=layers, base_width=args.base_width).to(device)
+    if world > 1:  # identical replicas
+        for p in model.parameters():
+            dist.broadcast(p.data, 0)
+    opt = FusedClipAdam(model.parameters(), lr=1e-3, max_norm=1.0)
+    engine = TrainEngine(model, opt, n_classes, device, layout=layout, grad_backend=args.grad_allreduce)
+
+    S = 2 ** args.scale
+    g = torch.Generator().manual_seed(1234 + rank)
+    n_host = 2  # rotate pinned host batches so a step never reuses the previous step's staging memory
+    host = []
+    for _ in range(n_host):
+        img = torch.rand((args.batch, 3, S, S, S), generator=g).pin_memory()
+        msk = torch.randint(0, n_classes, (args.batch, S, S, S), generator=g, dtype=torch.int16).pin_memory()
+        host.append((img, msk))
+    dev_batches = [(i.to(device), m.to(device)) for i, m in host]
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- warm-up -------------------------------------------------------------
+    for i in range(args.warmup):
+        engine.step(*dev_batches[i % n_host])
+    sync()
+    _lib.check_status()
+
+    # ---- device-timed region: inputs resident on the device ---------------------
+    launches0 = _lib.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            loss = engine.step(*dev_batches[i % n_host])
+        e1.record()
+        sync()
+        ms_total = max_over_ranks(e0.elapsed_time(e1))
+        launches = _lib.launch_count() - launches0
+
+        # ---- end-to-end region: pinned-host inputs in, loss value out, every step ----
+        for i in range(2):
+            float(engine.step(*host[i % n_host]).item())
+        sync()
+        e0.record()
+        for i in range(args.steps):
+            loss_val = float(engine.step(*host[i % n_host]).item())
+        e1.record()
+        sync()
+        ms_e2e = max_over_ranks(e0.elapsed_time(e1))
+    _lib.check_status()
+
+    global_batch = args.batch * layout.ddp_ranks
+    vox_per_step = global_batch * S ** 3
+    ms_per_step = ms_total / args.steps
+    value = vox_per_step / (ms_per_step / 1e3)
+    e2e_value = vox_per_step / (ms_e2e / args.steps / 1e3)
+    h2d = sum(t.numel() * t.element_size() for t in host[0])
+    base = baseline_value()
+    sp = layout.spatial_size
+    out = {
+        "metric": "3D U-Net train voxels/sec",
+        "value": value,
+        "unit": "voxels/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms_per_step,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": (value / base) if base else None,
+        "dtype": "bf16",
+        "data": "synthetic (random volumes and labels of the dataset's shape; random-init weights)",
+        "impl": "ours",
+        "config": {
+            "model": f"3D U-Net scale {args.scale}: {layers + 1} levels, base width {args.base_width}, GroupNorm(8), "
+                     f"{n_classes} classes, {sum(p.numel() for p in model.parameters())} params",
+            "global_batch": global_batch,
+            "seq_len": S ** 3,
+            "volume": [S, S, S],
+            "parallelism": (f"dp{layout.ddp_ranks}" + (f"xsp{sp}{list(layout.num_shards)}" if sp > 1 else "")),
+            "batch_per_replica": args.batch,
+            "grad_allreduce": args.grad_allreduce if world > 1 else "none",
+            "l2_policy": "inputs larger than L2 (activations of one step are several GB; two batches rotate)",
+            "final_loss": loss_val,
+        },
+        "clocks": clocks.summary(),
+        "e2e": {"value": e2e_value, "unit": "voxels/s", "ms_per_step": ms_e2e / args.steps,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+        "gpu_launches": launches,
+    }
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -389,6 +389,7 @@ static int finish_and_launch(IgemmParams& p, int cout_rows, cudaStream_t stream)
   int grid = q.num_tiles < g_sm_count ? q.num_tiles : g_sm_count;
   const size_t smem = (size_t)q.stages * q.stage_bytes + 1024;
   igemm_kernel<<<grid, 192, smem, stream>>>(q);
+  sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 

@@ -429,6 +429,7 @@ extern "C" int sb_conv_wgrad(const SbWgradArgs* a, cudaStream_t stream) {
   const int grid = p.n_outer * p.m_tiles * p.n_tiles * p.splits;
   const size_t smem = (size_t)p.stages * p.stage_bytes + 1024;
   wgrad_kernel<<<grid, 192, smem, stream>>>(p);
+  sb_count_launch(1);
   if (cudaGetLastError() != cudaSuccess) return SB_ERR_LAUNCH;
   ReduceParams& r = pl.r;
   r.ws = a->workspace;
@@ -440,5 +441,6 @@ extern "C" int sb_conv_wgrad(const SbWgradArgs* a, cudaStream_t stream) {
   const int threads = 256;
   const long long blocks = (r.total + threads - 1) / threads;
   wgrad_reduce_kernel<<<(unsigned)blocks, threads, 0, stream>>>(r);
+  sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }

@@ -422,6 +422,7 @@ extern "C" int sb_gn_stats(const SbGnArgs* a, cudaStream_t stream) {
   int rc = gn_fill(a, p);
   if (rc) return rc;
   gn_stats_kernel<<<dim3(p.nsplit, p.N), GN_THREADS, 0, stream>>>(p);
+  sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 
@@ -430,6 +431,7 @@ extern "C" int sb_gn_apply(const SbGnArgs* a, cudaStream_t stream) {
   int rc = gn_fill(a, p);
   if (rc) return rc;
   gn_apply_kernel<<<dim3(apply_blocks(p), p.N), GN_THREADS, 0, stream>>>(p);
+  sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 
@@ -438,6 +440,7 @@ extern "C" int sb_gn_bwd_partial(const SbGnArgs* a, cudaStream_t stream) {
   int rc = gn_fill(a, p);
   if (rc) return rc;
   gn_bwd_partial_kernel<<<dim3(p.nsplit, p.N), GN_THREADS, 0, stream>>>(p);
+  sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 
@@ -447,5 +450,6 @@ extern "C" int sb_gn_bwd_dx(const SbGnArgs* a, cudaStream_t stream) {
   if (rc) return rc;
   const size_t smem = (size_t)(4 * p.C + 2 * p.G) * sizeof(float);
   gn_bwd_dx_kernel<<<dim3(apply_blocks(p), p.N), GN_THREADS, smem, stream>>>(p);
+  sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }

@@ -97,6 +97,10 @@ typedef struct {
   int relu;
 } SbGnArgs;
 
+// number of kernels this library launched so far in the process
+long long sb_launch_count(void);
+void sb_count_launch(int n);
+
 int sb_gn_nsplit(int N, long long S, int C);
 int sb_gn_stats(const SbGnArgs* a, cudaStream_t stream);
 int sb_gn_apply(const SbGnArgs* a, cudaStream_t stream);

@@ -219,13 +219,14 @@ extern "C" int sb_loss_sums(const void* logits, const void* labels, int label_ki
   dim3 grid(blocks, N);
   const __nv_bfloat16* lg = (const __nv_bfloat16*)logits;
   switch (CP) {
-    case 8: loss_sums_kernel<8><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode); break;
-    case 16: loss_sums_kernel<16><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode); break;
-    case 24: loss_sums_kernel<24><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode); break;
-    case 32: loss_sums_kernel<32><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode); break;
+    case 8: loss_sums_kernel<8><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode); sb_count_launch(1); break;
+    case 16: loss_sums_kernel<16><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode); sb_count_launch(1); break;
+    case 24: loss_sums_kernel<24><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode); sb_count_launch(1); break;
+    case 32: loss_sums_kernel<32><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode); sb_count_launch(1); break;
     default: return SB_ERR_SHAPE;
   }
   loss_finalize_kernel<<<N, 128, 0, stream>>>(ws, sums, blocks, 3 * C + 2);
+  sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 
@@ -238,10 +239,10 @@ extern "C" int sb_loss_grad(const void* logits, const void* labels, int label_ki
   const __nv_bfloat16* lg = (const __nv_bfloat16*)logits;
   __nv_bfloat16* dl = (__nv_bfloat16*)dlogits;
   switch (CP) {
-    case 8: loss_grad_kernel<8><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S); break;
-    case 16: loss_grad_kernel<16><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S); break;
-    case 24: loss_grad_kernel<24><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S); break;
-    case 32: loss_grad_kernel<32><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S); break;
+    case 8: loss_grad_kernel<8><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S); sb_count_launch(1); break;
+    case 16: loss_grad_kernel<16><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S); sb_count_launch(1); break;
+    case 24: loss_grad_kernel<24><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S); sb_count_launch(1); break;
+    case 32: loss_grad_kernel<32><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S); sb_count_launch(1); break;
     default: return SB_ERR_SHAPE;
   }
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;

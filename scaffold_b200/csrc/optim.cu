@@ -85,7 +85,9 @@ extern "C" int sb_grad_norm(const float* g, long long n, float* partials, float*
   if ((reinterpret_cast<uintptr_t>(g) & 15) != 0) return SB_ERR_ALIGN;
   const int blocks = sb_opt_blocks(n);
   sumsq_partial_kernel<<<blocks, OPT_THREADS, 0, stream>>>(g, n, partials);
+  sb_count_launch(1);
   sumsq_finalize_kernel<<<1, 1, 0, stream>>>(partials, blocks, norm_out);
+  sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 
@@ -97,5 +99,6 @@ extern "C" int sb_adam_step(float* p, const float* g, float* m, float* v, long l
   const int blocks = sb_opt_blocks(n) * 2;
   adam_kernel<<<blocks, OPT_THREADS, 0, stream>>>(p, g, m, v, n, lr, b1, b2, eps, bc1, bc2_sqrt, max_norm, norm,
                                                   grad_scale);
+  sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }

@@ -132,6 +132,7 @@ extern "C" int sb_maxpool2_fwd(const void* x, void* y, int N, int D, int H, int 
   if (C % 8 != 0 || D < 2 || H < 2 || W < 2) return SB_ERR_SHAPE;
   const long long total = (long long)N * (D / 2) * (H / 2) * (W / 2) * (C / 8);
   maxpool2_fwd_kernel<<<pool_grid(total), 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, N, D, H, W, C);
+  sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 
@@ -141,7 +142,10 @@ extern "C" int sb_maxpool2_bwd(const void* gy, const void* x, const void* y, voi
   const long long total = (long long)N * (D / 2) * (H / 2) * (W / 2) * (C / 8);
   maxpool2_bwd_kernel<<<pool_grid(total), 256, 0, stream>>>((const __nv_bfloat16*)gy, (const __nv_bfloat16*)x,
                                                             (const __nv_bfloat16*)y, (__nv_bfloat16*)gx, N, D, H, W, C);
-  if ((D | H | W) & 1)
+  sb_count_launch(1);
+  if ((D | H | W) & 1) {
     maxpool2_bwd_tail_kernel<<<pool_grid((long long)N * D * H * W), 256, 0, stream>>>((__nv_bfloat16*)gx, N, D, H, W, C);
+    sb_count_launch(1);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }

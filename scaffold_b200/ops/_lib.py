@@ -117,6 +117,7 @@ _SIGNATURES = {
     "sb_convT_dgrad": ([C.POINTER(SbConvTArgs), _P], C.c_int),
     "sb_conv_wgrad": ([C.POINTER(SbWgradArgs), _P], C.c_int),
     "sb_conv_wgrad_workspace": ([C.POINTER(SbWgradArgs)], C.c_longlong),
+    "sb_launch_count": ([], C.c_longlong),
 }
 
 
@@ -127,6 +128,11 @@ def register(name: str, argtypes, restype=C.c_int) -> None:
         fn = getattr(_lib, name)
         fn.argtypes = argtypes
         fn.restype = restype
+
+
+def launch_count() -> int:
+    """Kernels launched by the native library so far in this process."""
+    return int(lib().sb_launch_count())
 
 
 def check(rc: int, what: str) -> None:
