@@ -39,7 +39,6 @@ struct IgemmParams {
   CUtensorMap mapB;
   int TH, TW, TD, TN;
   int KWS, KHS, n_outer, BK, BN;
-  int base_off_mode;
   int stages, stage_bytes, a_bytes, b_bytes, tx_bytes;  // a_bytes: offset of B inside a stage
   int N, D, H, W;  // output voxel grid (== the grid the tile bricks walk)
   int tiles_h, tiles_w, tiles_d, tiles_n, tiles_co, num_tiles;
@@ -136,7 +135,8 @@ __global__ void __launch_bounds__(192, 1) igemm_kernel(const __grid_constant__ I
       const uint32_t idesc = make_idesc_bf16(128, p.BN, 0, 0);
       const uint32_t swz = swizzle_code_for(rowb);
       const int rh = p.TH + p.KHS - 1;             // rows per w column of the A box
-      const uint32_t sbo = (uint32_t)rh * rowb;    // 8-row groups are one w step apart
+      // 8-row groups are contiguous unless the box carries an h halo (then one w step apart)
+      const uint32_t sbo = (uint32_t)(p.KHS > 1 ? rh : 8) * rowb;
       const uint32_t b_shift = (uint32_t)p.BN * rowb;
       uint32_t it = 0, tcount = 0;
       bool ok = true;
@@ -155,11 +155,10 @@ __global__ void __launch_bounds__(192, 1) igemm_kernel(const __grid_constant__ I
           const uint32_t sbm = sa + p.a_bytes;
           for (int kh = 0; kh < p.KHS; ++kh) {
             for (int kw = 0; kw < p.KWS; ++kw) {
-              const uint32_t a0 = sa + (uint32_t)(kw * rh + kh) * rowb;
+              const uint32_t a0 = sa + (uint32_t)(kw * (p.KHS > 1 ? rh : p.TH) + kh) * rowb;
               const uint32_t b0 = sbm + (uint32_t)(kh * p.KWS + kw) * b_shift;
               for (int k = 0; k < p.BK / 16; ++k) {
-                uint64_t da = make_smem_desc(a0 + k * 32u, 16u, sbo, swz);
-                if (p.base_off_mode) da |= (uint64_t)((a0 >> 7) & 7u) << 49;
+                const uint64_t da = make_smem_desc(a0 + k * 32u, 16u, sbo, swz);
                 const uint64_t db = make_smem_desc(b0 + k * 32u, 16u, 8u * rowb, swz);
                 tc_mma_bf16(acc, da, db, idesc, (ki | kh | kw | k) != 0 ? 1u : 0u);
               }
@@ -399,7 +398,16 @@ using namespace sb;
 
 // Stride-1 "same" convolution, k in {1,3}; also backward-data when the caller
 // packs the weights transposed and tap-flipped.
+namespace sb { int conv_plane_launch(const SbConvArgs* a, cudaStream_t stream); }
+
+// force_plain: 0 = automatic (plane-walk kernel when the shape is eligible, else this file's
+// generic kernel), 1 = generic kernel one tap per load, 2 = generic kernel with the w-shift
+// reuse, 3 = generic kernel with the (h, w)-shift reuse.
 extern "C" int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream) {
+  if (a->force_plain == 0) {
+    const int prc = conv_plane_launch(a, stream);
+    if (prc >= 0) return prc;
+  }
   int rc = device_setup();
   if (rc) return rc;
   IgemmParams p;
@@ -417,10 +425,7 @@ extern "C" int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream) {
   const bool can_shift = a->ksize == 3 && a->W >= 16 && a->H >= 8;
   const bool shift = can_shift && a->force_plain != 1;
   choose_brick(p, shift);
-  if (shift && a->force_plain >= 2) {
-    p.KHS = 3;
-    p.base_off_mode = a->force_plain == 3 ? 1 : 0;
-  }
+  if (shift && a->force_plain == 3) p.KHS = 3;
   const int taps = a->ksize * a->ksize * a->ksize;
   p.n_outer = taps / (p.KWS * p.KHS);
   p.maps_per_tap = nsrc;

@@ -373,6 +373,67 @@ __global__ void __launch_bounds__(GN_THREADS) gn_bwd_dx_kernel(const GnParams p)
   }
 }
 
+// ----------------------------------------------------------------------------
+// finalize: collapse the per-split partials of one rank into a single entry per
+// (n, g) / (n, c), in parallel (one warp per output, fixed merge tree), so the
+// streaming kernels start from O(1) statistics instead of walking every split.
+// ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(GN_THREADS) gn_stats_finalize_kernel(const float* __restrict__ part,
+                                                                       float* __restrict__ fin, int N, int G,
+                                                                       int nsplit) {
+  const int warp = (blockIdx.x * GN_THREADS + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= N * G) return;
+  const int n = warp / G, g = warp % G;
+  float gn = 0.f, gm = 0.f, g2 = 0.f;
+  for (int s = lane; s < nsplit; s += 32) {
+    const float* e = part + (((long long)n * nsplit + s) * G + g) * 3;
+    chan_merge(gn, gm, g2, e[0], e[1], e[2]);
+  }
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float on = __shfl_xor_sync(0xffffffffu, gn, o);
+    const float om = __shfl_xor_sync(0xffffffffu, gm, o);
+    const float o2 = __shfl_xor_sync(0xffffffffu, g2, o);
+    // merge (lower lane, higher lane) in that order on both sides: bitwise identical results
+    if (lane & o) {
+      float an = on, am = om, a2 = o2;
+      chan_merge(an, am, a2, gn, gm, g2);
+      gn = an; gm = am; g2 = a2;
+    } else {
+      chan_merge(gn, gm, g2, on, om, o2);
+    }
+  }
+  if (lane == 0) {
+    float* dst = fin + ((long long)n * G + g) * 3;
+    dst[0] = gn; dst[1] = gm; dst[2] = g2;
+  }
+}
+
+__global__ void __launch_bounds__(GN_THREADS) gn_bwd_finalize_kernel(const float* __restrict__ part,
+                                                                     float* __restrict__ fin, int N, int C,
+                                                                     int nsplit) {
+  const int warp = (blockIdx.x * GN_THREADS + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= N * C) return;
+  const int n = warp / C, c = warp % C;
+  float a = 0.f, b = 0.f;
+  for (int s = lane; s < nsplit; s += 32) {
+    const float2 e = *reinterpret_cast<const float2*>(part + (((long long)n * nsplit + s) * C + c) * 2);
+    a += e.x;
+    b += e.y;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    b += __shfl_xor_sync(0xffffffffu, b, o);
+  }
+  if (lane == 0) {
+    float* dst = fin + ((long long)n * C + c) * 2;
+    dst[0] = a; dst[1] = b;
+  }
+}
+
 static int gn_fill(const SbGnArgs* a, GnParams& p) {
   if (a->C % 8 != 0 || a->C % a->G != 0 || a->C > 2048 || a->G > 256) return SB_ERR_SHAPE;
   const int cg = a->C / a->G;
@@ -450,6 +511,22 @@ extern "C" int sb_gn_bwd_dx(const SbGnArgs* a, cudaStream_t stream) {
   if (rc) return rc;
   const size_t smem = (size_t)(4 * p.C + 2 * p.G) * sizeof(float);
   gn_bwd_dx_kernel<<<dim3(apply_blocks(p), p.N), GN_THREADS, smem, stream>>>(p);
+  sb_count_launch(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
+
+// fin: [N][G][3] (stats) / [N][C][2] (bwd) -- the single-split form the apply / dx kernels merge
+extern "C" int sb_gn_stats_finalize(const float* part, float* fin, int N, int G, int nsplit, cudaStream_t stream) {
+  const int warps = N * G;
+  gn_stats_finalize_kernel<<<(warps * 32 + GN_THREADS - 1) / GN_THREADS, GN_THREADS, 0, stream>>>(part, fin, N, G, nsplit);
+  sb_count_launch(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
+extern "C" int sb_gn_bwd_finalize(const float* part, float* fin, int N, int C, int nsplit, cudaStream_t stream) {
+  const int warps = N * C;
+  gn_bwd_finalize_kernel<<<(warps * 32 + GN_THREADS - 1) / GN_THREADS, GN_THREADS, 0, stream>>>(part, fin, N, C, nsplit);
   sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }

@@ -36,9 +36,11 @@ class SbGnArgs(C.Structure):
 
 for _n in ("sb_gn_stats", "sb_gn_apply", "sb_gn_bwd_partial", "sb_gn_bwd_dx"):
     _lib.register(_n, [C.POINTER(SbGnArgs), C.c_void_p], C.c_int)
+_lib.register("sb_gn_stats_finalize", [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p], C.c_int)
+_lib.register("sb_gn_bwd_finalize", [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p], C.c_int)
 
 
-def _base(x: torch.Tensor, w, b, groups: int, eps: float, relu: bool, shards: int) -> SbGnArgs:
+def _base(x: torch.Tensor, w, b, groups: int, eps: float, relu: bool, shards: int, nsplit: int = 0) -> SbGnArgs:
     n, d, h, wd, c = x.shape
     a = SbGnArgs()
     a.x = x.data_ptr()
@@ -46,7 +48,7 @@ def _base(x: torch.Tensor, w, b, groups: int, eps: float, relu: bool, shards: in
     a.N, a.C, a.G = n, c, groups
     a.S = d * h * wd
     a.S_total = a.S * shards
-    a.nsplit = _lib.lib().sb_gn_nsplit(n, a.S, c)
+    a.nsplit = nsplit or _lib.lib().sb_gn_nsplit(n, a.S, c)
     a.eps = eps
     a.relu = 1 if relu else 0
     return a
@@ -62,8 +64,9 @@ def partial_numel_bwd(x: torch.Tensor) -> int:
     return n * _lib.lib().sb_gn_nsplit(n, d * h * w, c) * c * 2
 
 
-def gn_stats(x, w, b, groups, eps, relu, part: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Pass 1: this rank's partial (count, mean, M2) per (n, split, group)."""
+def gn_stats(x, w, b, groups, eps, relu, part: Optional[torch.Tensor] = None,
+             fin: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Pass 1: this rank's (count, mean, M2) per (n, group), shape ``[N*G*3]`` (what peers exchange)."""
     a = _base(x, w, b, groups, eps, relu, 1)
     if part is None:
         part = torch.empty(partial_numel_fwd(x, groups), dtype=torch.float32, device=x.device)
@@ -71,12 +74,16 @@ def gn_stats(x, w, b, groups, eps, relu, part: Optional[torch.Tensor] = None) ->
     a.n_parts = 1
     a.parts[0] = part.data_ptr()
     _lib.check(_lib.lib().sb_gn_stats(C.byref(a), _lib.stream_ptr()), "sb_gn_stats")
-    return part
+    if fin is None:
+        fin = torch.empty(x.shape[0] * groups * 3, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().sb_gn_stats_finalize(part.data_ptr(), fin.data_ptr(), x.shape[0], groups, a.nsplit,
+                                               _lib.stream_ptr()), "sb_gn_stats_finalize")
+    return fin
 
 
 def gn_apply(x, w, b, groups, eps, relu, parts: Sequence[int], shards: int = 1):
     """Pass 2: merge ``parts`` (device pointers, own first) and normalise."""
-    a = _base(x, w, b, groups, eps, relu, shards)
+    a = _base(x, w, b, groups, eps, relu, shards, nsplit=1)
     n = x.shape[0]
     y = torch.empty_like(x)
     mean = torch.empty((n, groups), dtype=torch.float32, device=x.device)
@@ -94,7 +101,9 @@ def gn_forward(x, w, b, groups: int, eps: float = 1e-5, relu: bool = True):
     return gn_apply(x, w, b, groups, eps, relu, [part.data_ptr()])
 
 
-def gn_bwd_partial(dy, x, w, b, mean, rstd, groups, eps, relu, part: Optional[torch.Tensor] = None):
+def gn_bwd_partial(dy, x, w, b, mean, rstd, groups, eps, relu, part: Optional[torch.Tensor] = None,
+                   fin: Optional[torch.Tensor] = None):
+    """Backward pass 1: this rank's per-(n, channel) sums ``[N*C*2]`` (what peers exchange)."""
     a = _base(x, w, b, groups, eps, relu, 1)
     a.dy = dy.data_ptr()
     a.mean, a.rstd = mean.data_ptr(), rstd.data_ptr()
@@ -104,11 +113,15 @@ def gn_bwd_partial(dy, x, w, b, mean, rstd, groups, eps, relu, part: Optional[to
     a.n_parts = 1
     a.parts[0] = part.data_ptr()
     _lib.check(_lib.lib().sb_gn_bwd_partial(C.byref(a), _lib.stream_ptr()), "sb_gn_bwd_partial")
-    return part
+    if fin is None:
+        fin = torch.empty(x.shape[0] * x.shape[4] * 2, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().sb_gn_bwd_finalize(part.data_ptr(), fin.data_ptr(), x.shape[0], x.shape[4], a.nsplit,
+                                             _lib.stream_ptr()), "sb_gn_bwd_finalize")
+    return fin
 
 
 def gn_bwd_dx(dy, x, w, b, mean, rstd, groups, eps, relu, parts: Sequence[int], shards: int = 1):
-    a = _base(x, w, b, groups, eps, relu, shards)
+    a = _base(x, w, b, groups, eps, relu, shards, nsplit=1)
     a.dy = dy.data_ptr()
     a.mean, a.rstd = mean.data_ptr(), rstd.data_ptr()
     dx = torch.empty_like(x)

@@ -40,23 +40,29 @@ def pad_c(x, c):  # pad channel dim (dim 1) of NCDHW with zeros
 
 
 FWD_CASES = [
-    # N, D, H, W, Cin(list), Cout, k, force_plain
-    (1, 4, 16, 32, [64], 64, 3, False),
-    (1, 4, 16, 32, [64], 64, 3, True),
-    (2, 4, 8, 8, [128], 256, 3, False),
-    (1, 2, 16, 16, [64, 64], 64, 3, False),
-    (1, 2, 16, 16, [128, 64], 128, 3, True),
-    (1, 3, 12, 20, [64], 64, 3, False),
-    (1, 3, 12, 20, [32], 32, 3, False),
-    (1, 4, 16, 16, [3], 64, 3, False),
-    (2, 4, 4, 4, [64], 128, 3, False),
-    (1, 2, 16, 16, [64], 9, 1, False),
-    (1, 32, 32, 32, [64], 64, 3, False),
-    (1, 8, 8, 8, [512], 128, 3, False),
+    # N, D, H, W, Cin(list), Cout, k, kernel mode (0 auto / plane-walk, 1 plain, 2 w-shift, 3 hw-shift)
+    (1, 4, 16, 32, [64], 64, 3, 0),
+    (1, 4, 16, 32, [64], 64, 3, 1),
+    (1, 4, 16, 32, [64], 64, 3, 2),
+    (1, 4, 16, 32, [64], 64, 3, 3),
+    (2, 7, 24, 48, [64], 64, 3, 0),
+    (1, 5, 16, 16, [128], 256, 3, 0),
+    (1, 2, 16, 16, [64, 64], 64, 3, 2),
+    (2, 16, 64, 64, [64], 64, 3, 0),
+    (2, 4, 8, 8, [128], 256, 3, 0),
+    (1, 2, 16, 16, [64, 64], 64, 3, 0),
+    (1, 2, 16, 16, [128, 64], 128, 3, 1),
+    (1, 3, 12, 20, [64], 64, 3, 0),
+    (1, 3, 12, 20, [32], 32, 3, 0),
+    (1, 4, 16, 16, [3], 64, 3, 0),
+    (2, 4, 4, 4, [64], 128, 3, 0),
+    (1, 2, 16, 16, [64], 9, 1, 0),
+    (1, 32, 32, 32, [64], 64, 3, 0),
+    (1, 8, 8, 8, [512], 128, 3, 0),
 ]
 
 
-@pytest.mark.parametrize("case", FWD_CASES, ids=lambda c: "x".join(map(str, c[:4])) + f"_{c[4]}to{c[5]}_k{c[6]}{'_plain' if c[7] else ''}")
+@pytest.mark.parametrize("case", FWD_CASES, ids=lambda c: "x".join(map(str, c[:4])) + f"_{c[4]}to{c[5]}_k{c[6]}_m{c[7]}")
 def test_conv_fwd_bitwise(case):
     _lib, ck = _ck()
     n, d, h, w, cins, cout, k, plain = case
