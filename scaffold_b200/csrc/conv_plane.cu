@@ -146,9 +146,12 @@ __global__ void __launch_bounds__(224, 1) conv_plane_kernel(const __grid_constan
     }
   } else if (warp == 2) {
     // ------------------------------- MMA issuer -------------------------------
-    // One thread issues every MMA. Descriptors are kept as (lo, hi) words so that a
+    // The whole warp runs this loop with warp-uniform control flow (every wait result is
+    // voted on), so descriptor arithmetic stays in uniform registers; one elected lane
+    // issues the tcgen05 instructions. Descriptors are kept as (lo, hi) words so that a
     // new operand address is one integer add; all plane / k loops are unrolled.
-    if (lane == 0) {
+    {
+      const bool leader = elect_one();
       const uint32_t idesc = make_idesc_bf16(128, p.BN, 0, 0);
       const uint32_t swz = swizzle_code_for(rowb);
       const uint32_t a_hi = desc_hi((uint32_t)PL_RH * rowb, swz);
@@ -174,7 +177,7 @@ __global__ void __launch_bounds__(224, 1) conv_plane_kernel(const __grid_constan
           for (int kd = 0; kd < 3; ++kd) {
             for (int khw = 0; khw < 9 && ok; ++khw) {
               const int kh = khw / 3, kw = khw - kh * 3;
-              if (!mbar_wait(&b_full[b_slot], b_par, abort_flag, p.status, 23)) { ok = false; break; }
+              if (!__all_sync(0xffffffffu, mbar_wait(&b_full[b_slot], b_par, abort_flag, p.status, 23))) { ok = false; break; }
               tc_fence_after();
               const uint32_t b_lo = desc_lo(sb0 + b_slot * p.b_slot_bytes, 16u);
               const uint32_t tap_off = ((uint32_t)(kw * PL_RH + kh) * rowb) >> 4;
@@ -183,43 +186,47 @@ __global__ void __launch_bounds__(224, 1) conv_plane_kernel(const __grid_constan
               for (int t = 0; t < TD; ++t) {
                 const int j = t + kd;
                 if (j >= waited) {
-                  if (!mbar_wait(&a_full[pl_slot[j]], pl_par[j], abort_flag, p.status, 24)) { ok = false; break; }
+                  if (!__all_sync(0xffffffffu, mbar_wait(&a_full[pl_slot[j]], pl_par[j], abort_flag, p.status, 24))) { ok = false; break; }
                   tc_fence_after();
                   waited = j + 1;
                 }
                 const uint32_t acc_i = buf * TD + t;
                 if (kd == 0 && first) {
                   const uint32_t u = acc_uses[acc_i]++;
-                  if (!mbar_wait(&tempty[acc_i], (u & 1u) ^ 1u, abort_flag, p.status, 25)) { ok = false; break; }
+                  if (!__all_sync(0xffffffffu, mbar_wait(&tempty[acc_i], (u & 1u) ^ 1u, abort_flag, p.status, 25))) { ok = false; break; }
                   tc_fence_after();
                 }
                 const uint32_t a_lo = pl_lo[j] + tap_off;
                 const uint32_t acc = tmem_base + acc_i * p.BN;
 #pragma unroll
                 for (int k = 0; k < KSTEPS; ++k) {
-                  if (kd == 0 && k == 0)
-                    tc_mma_bf16_pred(acc, a_lo, a_hi, b_lo, b_hi, idesc, first ? 0u : 1u);
-                  else
-                    tc_mma_bf16_acc(acc, a_lo + 2u * k, a_hi, b_lo + 2u * k, b_hi, idesc);
+                  if (leader) {
+                    if (kd == 0 && k == 0)
+                      tc_mma_bf16_pred(acc, a_lo, a_hi, b_lo, b_hi, idesc, first ? 0u : 1u);
+                    else
+                      tc_mma_bf16_acc(acc, a_lo + 2u * k, a_hi, b_lo + 2u * k, b_hi, idesc);
+                  }
                 }
               }
               if (!ok) break;
-              tc_commit(&b_empty[b_slot]);
+              if (leader) tc_commit(&b_empty[b_slot]);
+              __syncwarp();
               if (++b_slot == (uint32_t)p.b_slots) { b_slot = 0; b_par ^= 1u; }
             }
             if (!ok) break;
             // planes that no later phase of this (job, cb) reads
             if (kd < 2) {
-              tc_commit(&a_empty[pl_slot[kd]]);
+              if (leader) tc_commit(&a_empty[pl_slot[kd]]);
             } else {
 #pragma unroll
-              for (int j = 2; j < planes; ++j) tc_commit(&a_empty[pl_slot[j]]);
+              for (int j = 2; j < planes; ++j)
+                if (leader) tc_commit(&a_empty[pl_slot[j]]);
             }
           }
           a_slot += planes;
           while (a_slot >= (uint32_t)p.a_slots) { a_slot -= p.a_slots; a_par ^= 1u; }
         }
-        if (ok) tc_commit(&tfull[buf]);
+        if (ok && leader) tc_commit(&tfull[buf]);
       }
     }
   } else {
