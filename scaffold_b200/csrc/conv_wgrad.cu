@@ -407,18 +407,61 @@ static int build_plan(const SbWgradArgs* a, Plan& pl, bool maps) {
 
 using namespace sb;
 
+namespace sb {
+long long wgrad_plane_workspace(const SbWgradArgs* a);
+int wgrad_plane_launch(const SbWgradArgs* a, cudaStream_t stream, int* splits_out);
+}
+
+// a->splits < 0 forces the generic kernel (tests); >= 0 prefers the plane kernel when eligible
 extern "C" long long sb_conv_wgrad_workspace(const SbWgradArgs* a) {
+  if (a->splits >= 0) {
+    const long long w = wgrad_plane_workspace(a);
+    if (w >= 0) return w;
+  }
   Plan pl;
   wg_setup();
-  if (build_plan(a, pl, false)) return -1;
+  SbWgradArgs generic = *a;
+  if (generic.splits < 0) generic.splits = -generic.splits - 1;
+  if (build_plan(&generic, pl, false)) return -1;
   return (long long)pl.p.splits * pl.p.T * pl.p.Mtot * pl.p.Ntot;
 }
 
 // real (unpadded) channel counts of the parameter are passed in dw_cout/dw_cin
+static int run_reduce(const SbWgradArgs* a, ReduceParams& r, cudaStream_t stream) {
+  r.ws = a->workspace;
+  r.dw = a->dw;
+  r.cout = a->dw_cout;
+  r.cin = a->dw_cin;
+  r.taps = a->ksize == 3 ? 27 : (a->ksize == 2 ? 8 : 1);
+  r.total = (long long)r.cout * r.cin * r.taps;
+  const int threads = 256;
+  const long long blocks = (r.total + threads - 1) / threads;
+  wgrad_reduce_kernel<<<(unsigned)blocks, threads, 0, stream>>>(r);
+  sb_count_launch(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
 extern "C" int sb_conv_wgrad(const SbWgradArgs* a, cudaStream_t stream) {
-  int rc = wg_setup();
+  int rc;
+  if (a->splits >= 0) {
+    int splits = 0;
+    rc = wgrad_plane_launch(a, stream, &splits);
+    if (rc > 0) return rc;
+    if (rc == 0) {
+      ReduceParams r;
+      memset(&r, 0, sizeof(r));
+      r.splits = splits; r.T = 27; r.Mtot = a->gy_c; r.Ntot = a->x_c[0] + a->x_c[1];
+      r.mode = 0;
+      r.accumulate = a->accumulate;
+      return run_reduce(a, r, stream);
+    }
+  }
+  rc = wg_setup();
   if (rc) return rc;
   Plan pl;
+  SbWgradArgs generic = *a;
+  if (generic.splits < 0) generic.splits = -generic.splits - 1;  // -1 -> automatic, -(k+1) -> k splits
+  a = &generic;
   rc = build_plan(a, pl, true);
   if (rc) return rc;
   WgradParams& p = pl.p;
@@ -431,16 +474,5 @@ extern "C" int sb_conv_wgrad(const SbWgradArgs* a, cudaStream_t stream) {
   wgrad_kernel<<<grid, 192, smem, stream>>>(p);
   sb_count_launch(1);
   if (cudaGetLastError() != cudaSuccess) return SB_ERR_LAUNCH;
-  ReduceParams& r = pl.r;
-  r.ws = a->workspace;
-  r.dw = a->dw;
-  r.cout = a->dw_cout;
-  r.cin = a->dw_cin;
-  r.taps = a->ksize == 3 ? 27 : (a->ksize == 2 ? 8 : 1);
-  r.total = (long long)r.cout * r.cin * r.taps;
-  const int threads = 256;
-  const long long blocks = (r.total + threads - 1) / threads;
-  wgrad_reduce_kernel<<<(unsigned)blocks, threads, 0, stream>>>(r);
-  sb_count_launch(1);
-  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+  return run_reduce(a, pl.r, stream);
 }

@@ -133,8 +133,15 @@ def test_convT_fwd_and_dgrad_bitwise(shape):
 
 WGRAD_CASES = [
     # N, D, H, W, Cin(list), Cout, k, splits
+    # splits: 0 automatic, k > 0 fixed; negative forces the generic kernel (-1 automatic, -(k+1) fixed k)
     (1, 4, 16, 32, [64], 64, 3, 0),
     (1, 4, 16, 32, [64], 64, 3, 3),
+    (1, 4, 16, 32, [64], 64, 3, -1),
+    (1, 4, 16, 32, [64], 64, 3, -4),
+    (1, 2, 16, 16, [64, 64], 64, 3, -1),
+    (1, 2, 16, 16, [128], 128, 3, -1),
+    (2, 3, 16, 32, [32, 32], 32, 3, 0),
+    (2, 5, 24, 40, [64], 128, 3, 2),
     (1, 2, 16, 16, [64, 64], 64, 3, 0),
     (1, 2, 16, 16, [64], 128, 3, 0),
     (1, 2, 16, 16, [128], 128, 3, 0),
