@@ -13,13 +13,28 @@ import torch.nn.functional as F
 AMP_DTYPE = torch.bfloat16
 
 
+_aten_only = [False]
+
+
+class aten_only:
+    """Context manager: route every module through ATen (the oracle of the parity tests)."""
+
+    def __enter__(self):
+        self._old = _aten_only[0]
+        _aten_only[0] = True
+        return self
+
+    def __exit__(self, *exc):
+        _aten_only[0] = self._old
+
+
 def use_cuda_kernels(x: torch.Tensor) -> bool:
     """True when the sm_100a kernel path applies: CUDA tensor, bf16 or autocast-to-bf16."""
-    if not x.is_cuda:
+    if not x.is_cuda or _aten_only[0]:
         return False
     if x.dtype == torch.bfloat16:
         return True
-    return torch.is_autocast_enabled() and torch.get_autocast_gpu_dtype() == torch.bfloat16
+    return torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16
 
 
 def to_vm(x: torch.Tensor, pad16: bool = False) -> torch.Tensor:
