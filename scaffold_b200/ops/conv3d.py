@@ -125,6 +125,10 @@ class Conv3d(nn.Conv3d):
         super().__init__(*args, **kwargs)
         self._cache = _PackCache()
         self._cache_b = _PackCache()
+        self._spatial = None  # parallel.spatial.SpatialContext when the volume is sharded
+
+    def set_spatial(self, ctx) -> None:
+        self._spatial = ctx
 
     def _real_in_channels(self, src_c: Sequence[int]) -> List[int]:
         """Real (unpadded) channel count of each source; only a single source may be padded."""
@@ -150,6 +154,12 @@ class Conv3d(nn.Conv3d):
             out = from_vm(y)
             return out if y.shape[4] == self.out_channels else out[:, : self.out_channels]
         xin = xs[0] if len(xs) == 1 else torch.cat([t.to(xs[0].dtype) for t in xs], dim=1)
+        sp = self._spatial
+        if sp is not None and sp.size > 1 and self.kernel_size[0] > 1:
+            # sharded volume: neighbours' boundary planes replace the zero padding on the split dims
+            xin = sp.halo_pad(xin, self.kernel_size[0] // 2)
+            return F.conv3d(xin, self.weight, self.bias, self.stride, sp.conv_padding(self.kernel_size[0]),
+                            self.dilation, self.groups)
         return super().forward(xin)
 
     def forward_padded(self, x) -> torch.Tensor:

@@ -1,0 +1,378 @@
+"""Training loop: datasets, samplers, optimizer/scheduler, warm-up, epochs, CSV, checkpoints.
+
+Public surface kept from ``PyTorchTrainer`` (ScaFFold/utils/trainer.py:366-1273):
+``Trainer(model, config, device, log)`` with ``cleanup_or_resume()``, ``warmup()``
+and ``train(profiler)``; ``train_stats.csv`` with the columns ``epoch, epoch_loss,
+overall_loss, val_loss_epoch, val_loss_avg, train_dice, val_dice, epoch_duration,
+optimizer_steps, total_optimizer_steps``; training runs until the validation
+Dice reaches ``target_dice`` (or ``epochs``); epoch metrics are sample-weighted
+sums reduced over the data-parallel replicas only (the spatial reduction already
+happened inside loss and metric); the per-minibatch time is measured with CUDA
+events, maximised over ranks and reported as a median, from which the
+voxels-per-second figure is derived.
+"""
+from __future__ import annotations
+
+import math
+import os
+import statistics
+import time
+from pathlib import Path
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+from torch.utils.data import DataLoader, DistributedSampler, Sampler
+
+from ..data.dataset import FractalDataset, SpatialShardSpec
+from ..ops.optim import FusedClipAdam
+from ..utils import dist as D
+from ..utils.log import gather_and_print_mem
+from ..utils.perf import adiak_value, begin_code_region, end_code_region, region
+from .checkpoint import CheckpointManager
+from .engine import TrainEngine
+from .evaluate import evaluate
+
+CSV_COLUMNS = ["epoch", "epoch_loss", "overall_loss", "val_loss_epoch", "val_loss_avg", "train_dice", "val_dice",
+               "epoch_duration", "optimizer_steps", "total_optimizer_steps"]
+
+
+class UnpaddedDistributedSampler(Sampler):
+    """Contiguous, unpadded split: every sample goes to exactly one replica (ranks may get uneven counts)."""
+
+    def __init__(self, dataset, num_replicas: int, rank: int):
+        n = len(dataset)
+        base, rem = divmod(n, num_replicas)
+        start = rank * base + min(rank, rem)
+        self.indices = list(range(start, start + base + (1 if rank < rem else 0)))
+
+    def __iter__(self):
+        return iter(self.indices)
+
+    def __len__(self):
+        return len(self.indices)
+
+    def set_epoch(self, epoch):  # order is fixed; present for API parity
+        return None
+
+
+def sample_ce_weight_indices(n_train: int, fraction: float) -> List[int]:
+    count = max(1, min(n_train, int(math.ceil(n_train * float(fraction)))))
+    step = n_train / count
+    return sorted({min(n_train - 1, int(i * step)) for i in range(count)})
+
+
+def compute_ce_class_weights(train_set, n_categories: int, device, sample_fraction: float = 0.1, log=None):
+    """Background vs foreground inverse-frequency weights from a sample of training masks, summed over ranks."""
+    num_classes = n_categories + 1
+    weights = torch.ones(num_classes, device=device, dtype=torch.float32)
+    n_train = len(train_set)
+    if n_train == 0:
+        if log is not None:
+            log.warning("Training set is empty while computing CE class weights. Falling back to uniform weights.")
+        return weights
+    idx = sample_ce_weight_indices(n_train, sample_fraction)
+    counts = torch.zeros(num_classes, dtype=torch.long)
+    for i in idx:
+        mask = train_set.load_mask_only(i) if hasattr(train_set, "load_mask_only") else train_set[i]["mask"]
+        counts += torch.bincount(mask.reshape(-1).long(), minlength=num_classes)[:num_classes]
+    counts = counts.to(device)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(counts)
+    bg, fg = int(counts[0].item()), int(counts[1:].sum().item())
+    if bg > 0 and fg > 0:
+        weights[0] = (bg + fg) / bg
+        weights[1:] = (bg + fg) / fg
+    elif log is not None:
+        log.warning("Sampled masks did not contain both background and foreground voxels. Falling back to uniform "
+                    "CE weights.")
+    if log is not None:
+        log.info("CE weights estimated from %d training masks (sample_fraction=%s): background_voxels=%d "
+                 "foreground_voxels=%d weights=%s", len(idx), sample_fraction, bg, fg, weights.cpu().tolist())
+    return weights
+
+
+def _collate(batch):
+    return {"image": torch.stack([b["image"] for b in batch]), "mask": torch.stack([b["mask"] for b in batch])}
+
+
+class Trainer:
+    def __init__(self, model, config, device, log, layout=None, spatial=None):
+        self.model, self.config, self.device, self.log = model, config, torch.device(device), log
+        self.layout, self.spatial = layout, spatial
+        self.world_rank = D.get_world_rank()
+        self.n_classes = int(config.n_categories) + 1
+        self.run_dir = Path(config.run_dir)
+        self.outfile_path = self.run_dir / "train_stats.csv"
+        self.start_epoch, self.start_val_dice = 1, 0.0
+        self.global_step = 0
+        self.total_optimizer_steps = 0
+        self._setup_data()
+        self._setup_optimization()
+        self.checkpoints = CheckpointManager(self.run_dir, config.checkpoint_dir, getattr(config, "async_save", False),
+                                             log)
+
+    # -- set-up -------------------------------------------------------------------
+    def _setup_data(self) -> None:
+        cfg = self.config
+        root = Path(cfg.dataset_dir)
+        spec = SpatialShardSpec.from_layout(self.layout) if self.layout is not None else SpatialShardSpec()
+        self.train_set = FractalDataset(root / "volumes" / "training", root / "masks" / "training", str(root), spec)
+        self.val_set = FractalDataset(root / "volumes" / "validation", root / "masks" / "validation", str(root), spec)
+        for ds in (self.train_set, self.val_set):
+            ds.check_ids_across_ranks()
+        replicas = self.layout.ddp_ranks if self.layout is not None else D.get_world_size()
+        replica = self.layout.ddp_ind if self.layout is not None else D.get_world_rank()
+        self.n_train, self.n_val = len(self.train_set), len(self.val_set)
+        bs = int(cfg.local_batch_size)
+        if self.n_train < replicas * 1:
+            raise ValueError(
+                f"The training split has {self.n_train} volume(s) but there are {replicas} data-parallel replicas: "
+                "some replica would train on nothing. Use fewer ranks, more spatial shards, or a larger dataset.")
+        self.train_sampler = DistributedSampler(self.train_set, num_replicas=replicas, rank=replica, shuffle=True,
+                                                seed=int(cfg.training_seed))
+        self.val_sampler = UnpaddedDistributedSampler(self.val_set, replicas, replica)
+        workers = int(cfg.dataloader_num_workers)
+        common = dict(num_workers=workers, pin_memory=self.device.type == "cuda", collate_fn=_collate,
+                      persistent_workers=workers > 0)
+        if workers > 0:
+            common["prefetch_factor"] = 2
+        self.train_loader = DataLoader(self.train_set, batch_size=bs, sampler=self.train_sampler, drop_last=False,
+                                       **common)
+        self.val_loader = DataLoader(self.val_set, batch_size=bs, sampler=self.val_sampler, drop_last=False, **common)
+        self.global_batch = bs * replicas
+        adiak_value("global_batch_size", self.global_batch)
+
+    def _setup_optimization(self) -> None:
+        cfg = self.config
+        params = [p for p in self.model.parameters() if p.requires_grad]
+        if cfg.optimizer == "ADAM":
+            self.optimizer = FusedClipAdam(params, lr=cfg.starting_learning_rate, max_norm=1.0)
+        elif cfg.optimizer == "SGD":
+            self.optimizer = torch.optim.SGD(params, lr=cfg.starting_learning_rate)
+        else:
+            self.optimizer = torch.optim.RMSprop(params, lr=cfg.starting_learning_rate, foreach=True)
+        self.scheduler = torch.optim.lr_scheduler.CosineAnnealingWarmRestarts(
+            self.optimizer, T_0=int(cfg.T_0), T_mult=int(cfg.T_mult), eta_min=float(cfg.min_learning_rate))
+        self.grad_scaler = None  # bf16 autocast needs no loss scaling
+        self.ce_class_weights = compute_ce_class_weights(self.train_set, int(cfg.n_categories), self.device,
+                                                         float(cfg.ce_weight_sample_fraction), self.log)
+        self.engine = TrainEngine(self.model, self.optimizer, self.n_classes, self.device, layout=self.layout,
+                                  spatial=self.spatial, class_weights=self.ce_class_weights,
+                                  amp=bool(cfg.torch_amp), grad_backend=getattr(cfg, "grad_allreduce", "nccl"))
+
+    # -- reductions -----------------------------------------------------------------
+    def _all_reduce_data_parallel(self, t: torch.Tensor) -> None:
+        if not dist.is_initialized() or dist.get_world_size() == 1:
+            return
+        if self.layout is not None:
+            if self.layout.ddp_ranks > 1:
+                dist.all_reduce(t, group=self.layout.ddp_group)
+        else:
+            dist.all_reduce(t)
+
+    def _median_minibatch_time(self, events) -> Optional[float]:
+        """Per-batch CUDA-event times, max over ranks per batch, then the median (seconds)."""
+        if not events:
+            return None
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / 1e3 for a, b in events], device=self.device)
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            sizes = [None] * dist.get_world_size()
+            dist.all_gather_object(sizes, int(t.numel()), group=D.control_group())
+            n = min(sizes)
+            t = t[:n].contiguous()
+            if n == 0:
+                return None
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(statistics.median(t.cpu().tolist()))
+
+    # -- resume ------------------------------------------------------------------------
+    def cleanup_or_resume(self) -> None:
+        cfg = self.config
+        resumed = None
+        if cfg.train_from_scratch and not getattr(cfg, "restart", False):
+            self.checkpoints.wipe()
+        else:
+            resumed = self.checkpoints.load(self.model, self.optimizer, self.scheduler)
+        if resumed is not None:
+            self.start_epoch = int(resumed["epoch"]) + 1
+            self.start_val_dice = float(resumed.get("val_dice", 0.0) or 0.0)
+            self.global_step = int(resumed.get("global_step", 0))
+            self.total_optimizer_steps = int(resumed.get("total_optimizer_steps", 0))
+            self.log.info("resumed from %s: next epoch %d, val dice %.6f", resumed.get("_loaded_from"),
+                          self.start_epoch, self.start_val_dice)
+        if self.world_rank == 0:
+            self._prepare_csv(resumed is not None)
+        D.barrier()
+
+    def _prepare_csv(self, resumed: bool) -> None:
+        """Fresh run: header only. Resume: keep the rows of epochs before ``start_epoch``."""
+        rows = []
+        if resumed and self.outfile_path.exists():
+            with open(self.outfile_path) as f:
+                for line in f.read().splitlines()[1:]:
+                    try:
+                        if int(line.split(",")[0]) < self.start_epoch:
+                            rows.append(line)
+                    except ValueError:
+                        continue
+        tmp = self.outfile_path.with_suffix(".csv.tmp")
+        with open(tmp, "w", newline="") as f:
+            f.write(",".join(CSV_COLUMNS) + "\n")
+            for line in rows:
+                f.write(line + "\n")
+        os.replace(tmp, self.outfile_path)
+
+    # -- warm-up -------------------------------------------------------------------------
+    def warmup(self) -> None:
+        """Run ``warmup_batches`` real steps (also a ragged final batch shape), then restore every state."""
+        n = int(self.config.warmup_batches or 0)
+        if n <= 0:
+            return
+        snap = CheckpointManager.snapshot(self.model, self.optimizer, self.scheduler)
+        self.model.train()
+        done = 0
+        ragged = self.n_train_local() % int(self.config.local_batch_size)
+        with region("warmup"):
+            while done < n:
+                for batch in self.train_loader:
+                    self.engine.step(batch["image"], batch["mask"])
+                    done += 1
+                    if done >= n:
+                        break
+            if ragged:
+                batch = next(iter(self.train_loader))
+                self.engine.step(batch["image"][:ragged], batch["mask"][:ragged])
+            if self.device.type == "cuda":
+                torch.cuda.synchronize()
+        CheckpointManager.restore(snap, self.model, self.optimizer, self.scheduler)
+        D.barrier()
+
+    def n_train_local(self) -> int:
+        return len(self.train_sampler)
+
+    # -- the loop ---------------------------------------------------------------------------
+    def train(self, profiler=None) -> dict:
+        cfg = self.config
+        epoch, val_score = self.start_epoch, self.start_val_dice
+        epoch_times, minibatch_times = [], []
+        last_ckpt_epoch, trained_any = None, False
+        val_loss_avg = float("inf")
+        vox_per_batch = self.global_batch * int(cfg.vol_size) ** 3
+        start = time.time()
+        csv = open(self.outfile_path, "a", newline="") if self.world_rank == 0 else None
+        try:
+            while val_score < cfg.target_dice:
+                if cfg.epochs != -1 and epoch > cfg.epochs:
+                    self.log.warning("Maximum epochs reached '%s'. Concluding training early (may have not converged).",
+                                     cfg.epochs)
+                    break
+                t0 = time.time()
+                self.train_sampler.set_epoch(epoch)
+                self.val_sampler.set_epoch(epoch)
+                self.model.train()
+                loss_sum = torch.zeros((), device=self.device)
+                dice_sum = torch.zeros((), device=self.device)
+                n_samples, steps, events = 0, 0, []
+                full_batches = self.n_train_local() // int(cfg.local_batch_size)
+                begin_code_region("batch_loop")
+                for bi, batch in enumerate(self.train_loader):
+                    timed = self.device.type == "cuda" and bi < full_batches
+                    if timed:
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record()
+                    with region("run_training_batch"):
+                        bs = batch["image"].shape[0]
+                        loss = self.engine.step(batch["image"], batch["mask"])
+                    if timed:
+                        e1.record()
+                        events.append((e0, e1))
+                    if epoch == self.start_epoch and bi == 0:
+                        gather_and_print_mem(self.log, "first_batch", self.device)
+                    loss_sum += loss * bs
+                    dice_sum += self.engine.last_dice * bs
+                    n_samples += bs
+                    steps += 1
+                    self.global_step += 1
+                    self.total_optimizer_steps += 1
+                    if profiler is not None:
+                        profiler.step()
+                end_code_region("batch_loop")
+                info = torch.stack([loss_sum, dice_sum, torch.tensor(float(n_samples), device=self.device)]).float()
+                self._all_reduce_data_parallel(info)
+                g_samples = max(info[2].item(), 1.0)
+                epoch_loss_total = info[0].item()
+                overall_loss = epoch_loss_total / g_samples
+                train_dice = info[1].item() / g_samples
+
+                d_sum, v_loss_epoch, _, _, n_val = evaluate(self.engine, self.val_loader, progress=self.world_rank == 0)
+                vinfo = torch.tensor([d_sum, v_loss_epoch, float(n_val)], device=self.device, dtype=torch.float32)
+                self._all_reduce_data_parallel(vinfo)
+                g_val = max(vinfo[2].item(), 1.0)
+                val_score = vinfo[0].item() / g_val
+                v_loss_epoch = vinfo[1].item()
+                val_loss_avg = v_loss_epoch / g_val
+                if not (math.isfinite(overall_loss) and math.isfinite(val_loss_avg)):
+                    raise ValueError(f"Non-finite loss at epoch {epoch} (train_loss={overall_loss}, "
+                                     f"val_loss={val_loss_avg}): training diverged, aborting before checkpointing.")
+                if not cfg.disable_scheduler:
+                    self.scheduler.step()
+                duration = time.time() - t0
+                epoch_times.append(duration)
+                mb = self._median_minibatch_time(events)
+                if mb is not None:
+                    minibatch_times.append(mb)
+                lr = self.optimizer.param_groups[0]["lr"]
+                self.log.info(" epoch %d | train_loss=%.6f | val_loss=%.6f | train_dice_score %.6f | val_dice_score "
+                              "%.6f | lr %.8f | optimizer_steps %d | total_optimizer_steps %d", epoch, overall_loss,
+                              val_loss_avg, train_dice, val_score, lr, steps, self.total_optimizer_steps)
+                if csv is not None:
+                    csv.write(",".join(str(v) for v in (epoch, epoch_loss_total, overall_loss, v_loss_epoch,
+                                                         val_loss_avg, train_dice, val_score, duration, steps,
+                                                         self.total_optimizer_steps)) + "\n")
+                    csv.flush()
+                    extra = (f" Median of minibatch times: {mb:.6f} seconds ({vox_per_batch / mb / 1e6:.2f} "
+                             f"Mvoxel/s)." if mb else "")
+                    self.log.info("Epoch %s completed in %.6f seconds. Total train time so far: %.6f seconds.%s",
+                                  epoch, duration, time.time() - start, extra)
+                with region("checkpoint"):
+                    if cfg.checkpoint_interval > 0 and epoch % cfg.checkpoint_interval == 0:
+                        self._save(epoch, val_loss_avg, val_score)
+                        last_ckpt_epoch = epoch
+                epoch += 1
+                trained_any = True
+                if math.isnan(val_score):
+                    raise ValueError("Invalid value (NaN) encountered in dice score computation")
+        finally:
+            if csv is not None:
+                csv.close()
+        completed = epoch - 1
+        if not trained_any:
+            self.log.warning("No new epoch was trained (start epoch %s, 'epochs' %s, starting val dice %s vs "
+                             "target_dice %s): this run had no epoch left to run, and no checkpoint was written.",
+                             self.start_epoch, cfg.epochs, self.start_val_dice, cfg.target_dice)
+        elif cfg.checkpoint_interval > 0 and completed >= 1 and last_ckpt_epoch != completed:
+            self._save(completed, val_loss_avg, val_score)
+        self.checkpoints.finalize_saves()
+        out = {"final_epochs": completed, "total_optimizer_steps": self.total_optimizer_steps, "val_dice": val_score}
+        if epoch_times:
+            out["epoch_time_s"] = statistics.median(epoch_times)
+            adiak_value("epoch_time_s", out["epoch_time_s"])
+            self.log.info("Median of epoch times: %.6f seconds.", out["epoch_time_s"])
+        if minibatch_times:
+            out["minibatch_time_s"] = statistics.median(minibatch_times)
+            out["voxels_per_second"] = vox_per_batch / out["minibatch_time_s"]
+            adiak_value("minibatch_time_s", out["minibatch_time_s"])
+            adiak_value("voxels_per_second", out["voxels_per_second"])
+            self.log.info("Median of epoch minibatch time medians: %.6f seconds (%.2f Mvoxel/s).",
+                          out["minibatch_time_s"], out["voxels_per_second"] / 1e6)
+        adiak_value("final_epochs", completed)
+        adiak_value("total_optimizer_steps", self.total_optimizer_steps)
+        return out
+
+    def _save(self, epoch: int, val_loss_avg: float, val_dice: float) -> None:
+        extras = {"train_mask_values": self.train_set.mask_values, "global_step": self.global_step,
+                  "total_optimizer_steps": self.total_optimizer_steps, "val_dice": val_dice}
+        self.checkpoints.save(epoch, val_loss_avg, self.model, self.optimizer, self.scheduler, self.grad_scaler,
+                              extras)
