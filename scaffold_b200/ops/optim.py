@@ -71,7 +71,7 @@ class FusedClipAdam(torch.optim.Adam):
         self._norm = None
         self._partials = None
         self._steps = 0
-        self.grad_scale = 1.0  # multiplied into every gradient before clipping (reducer averaging)
+        self.reduce_scale = 1.0  # factor applied to every gradient before clipping (reducer averaging)
 
     # -- flat state -------------------------------------------------------
     def _ensure_flat(self) -> bool:
@@ -138,9 +138,9 @@ class FusedClipAdam(torch.optim.Adam):
             # CPU / mixed placement: clip with torch, step with the stock implementation
             if self.max_norm is not None:
                 ps = [p for g in self.param_groups for p in g["params"] if p.grad is not None]
-                if self.grad_scale != 1.0:
+                if self.reduce_scale != 1.0:
                     for p in ps:
-                        p.grad.mul_(self.grad_scale)
+                        p.grad.mul_(self.reduce_scale)
                 torch.nn.utils.clip_grad_norm_(ps, self.max_norm)
             return super().step(closure)
         f = self.flat
@@ -156,7 +156,7 @@ class FusedClipAdam(torch.optim.Adam):
         b1, b2 = g["betas"]
         _lib.check(L.sb_adam_step(f.data.data_ptr(), f.grad.data_ptr(), self._m.data_ptr(), self._v.data_ptr(),
                                   f.numel, float(g["lr"]), float(b1), float(b2), float(g["eps"]), self._steps,
-                                  max_norm, self._norm.data_ptr(), float(self.grad_scale), s), "sb_adam_step")
+                                  max_norm, self._norm.data_ptr(), float(self.reduce_scale), s), "sb_adam_step")
         self._step_t.fill_(float(self._steps))
         bump_weights_epoch()
         return None

@@ -37,7 +37,7 @@ class TrainEngine:
         params = [p for p in model.parameters() if p.requires_grad]
         self.reducer = GradReducer(layout, flat=self.flat, params=params, backend=grad_backend)
         if isinstance(optimizer, FusedClipAdam):
-            optimizer.grad_scale = self.reducer.scale
+            optimizer.reduce_scale = self.reducer.scale
         self.last_ce = self.last_dice = None
 
     # -- data movement --------------------------------------------------------

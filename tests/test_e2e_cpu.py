@@ -1,0 +1,46 @@
+"""End-to-end plumbing on CPU/gloo at scale 4: one rank, two spatial shards, two replicas, resume."""
+import csv
+from pathlib import Path
+
+import pytest
+
+from helpers.launch import ROOT, results, torchrun_gloo
+
+SCRIPT = ROOT / "tests" / "helpers" / "rank_scripts" / "benchmark_tiny.py"
+
+
+def _run(tmp_path, nproc, shards_w, *extra):
+    proc = torchrun_gloo(SCRIPT, nproc, [str(tmp_path), str(shards_w), *extra])
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    return results(proc.stdout)
+
+
+@pytest.mark.slow
+def test_two_spatial_shards_match_one_rank(tmp_path):
+    one = _run(tmp_path, 1, 1)
+    two = _run(tmp_path, 2, 2)
+    assert one["final_epochs"] == ["2"] and two["final_epochs"] == ["2"]
+    for key in ("epoch1", "epoch2"):
+        a = [float(v) for v in one[key][0].split()]
+        b = [float(v) for v in two[key][0].split()]
+        # train loss, validation loss: fp32-level agreement; hard Dice: a few argmax near-ties may flip
+        assert abs(a[0] - b[0]) <= 5e-4 * max(1.0, abs(a[0])), (key, a, b)
+        assert abs(a[1] - b[1]) <= 5e-4 * max(1.0, abs(a[1])), (key, a, b)
+        assert abs(a[2] - b[2]) <= 3e-3, (key, a, b)
+    files = one["files"][0]
+    for name in ("train_stats.csv", "checkpoints", "run_metadata.yaml", "figures"):
+        assert name in files
+
+
+@pytest.mark.slow
+def test_two_replicas_run_and_resume(tmp_path):
+    first = _run(tmp_path, 2, 1, "1", "{job_name: dp}")
+    assert first["final_epochs"] == ["1"]
+    run_dir = tmp_path / "run_w2_s1_dp"
+    assert (run_dir / "checkpoints" / "checkpoint_last.pth").exists()
+    again = _run(tmp_path, 2, 1, "3", f"{{job_name: dp, train_from_scratch: 0, restart: true, run_dir: '{run_dir}'}}")
+    assert again["final_epochs"] == ["3"]
+    with open(run_dir / "train_stats.csv") as f:
+        epochs = [int(r["epoch"]) for r in csv.DictReader(f)]
+    assert epochs == [1, 2, 3]  # the first epoch's row survived, training continued at epoch 2
+    assert again["epoch1"] == first["epoch1"]
