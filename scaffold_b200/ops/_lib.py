@@ -161,6 +161,17 @@ SITES = {
     11: "wgrad producer waiting for a free stage",
     12: "wgrad MMA waiting for operands",
     13: "wgrad epilogue waiting for the accumulator",
+    21: "plane conv: activation producer waiting for a free slot",
+    22: "plane conv: weight producer waiting for a free slot",
+    23: "plane conv: MMA waiting for a weight tap",
+    24: "plane conv: MMA waiting for an activation plane",
+    25: "plane conv: MMA waiting for a free accumulator",
+    26: "plane conv: epilogue waiting for the accumulators",
+    31: "plane wgrad: producer waiting for a free stage",
+    32: "plane wgrad: MMA waiting for operands",
+    33: "plane wgrad: epilogue waiting for the accumulators",
+    41: "gradient all-reduce: waiting for the peers' gradients",
+    42: "gradient all-reduce: waiting for the peers' completion",
 }
 
 

@@ -48,6 +48,15 @@ class FlatBuffers:
             p.data = view
             p.grad = self.grad[o:o + p.numel()].view_as(p)
 
+    def rehome_grad(self, new_grad: torch.Tensor) -> None:
+        """Move the gradient buffer into ``new_grad`` (e.g. peer-visible memory) and re-point every ``.grad``."""
+        if new_grad.numel() != self.numel or new_grad.dtype != torch.float32:
+            raise ValueError("replacement gradient buffer must be fp32 with the same number of elements")
+        new_grad.copy_(self.grad)
+        self.grad = new_grad
+        for p, o in zip(self.params, self.offsets):
+            p.grad = self.grad[o:o + p.numel()].view_as(p)
+
     def rebind_grads(self) -> None:
         """Point every ``.grad`` back at the flat buffer (after ``zero_grad(set_to_none=True)``)."""
         for p, o in zip(self.params, self.offsets):

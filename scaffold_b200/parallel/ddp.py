@@ -31,7 +31,8 @@ class GradReducer:
         if backend == "fused" and self.world > 1 and flat is not None:
             try:
                 from .fused_allreduce import FusedAllReduce
-                self._fused = FusedAllReduce(flat.grad, self.world)
+                self._fused = FusedAllReduce(flat.numel)
+                flat.rehome_grad(self._fused.grad)  # gradients now accumulate straight into peer-visible memory
             except Exception as exc:  # documented degradation: the NCCL path is always correct
                 import logging
                 logging.getLogger("scaffold").warning("fused gradient all-reduce unavailable (%s); using NCCL", exc)
