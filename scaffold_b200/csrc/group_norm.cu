@@ -530,3 +530,57 @@ extern "C" int sb_gn_bwd_finalize(const float* part, float* fin, int N, int C, i
   sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
+
+// ----------------------------------------------------------------------------
+// Allocation-free forward (declared in no_alloc.h)
+// ----------------------------------------------------------------------------
+#include "no_alloc.h"
+
+namespace sb {
+// Scratch of the allocation-free entry point: partial statistics, then the per-sample
+// finals, then (when the caller passes none) mean / rstd. In host code this NAME is only a
+// handle for cudaGetSymbolAddress; kernels get the resolved device address.
+static __device__ __align__(256) float g_gn_noalloc_scratch[SB_GN_NOALLOC_SCRATCH_FLOATS + 2 * 256 * 64];
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* g_gn_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+}  // namespace sb
+
+extern "C" int sb_gn_forward_noalloc(const void* x, void* y, const float* w, const float* b, float* mean,
+                                     float* rstd, int N, long long S, int C, int G, float eps, int relu,
+                                     cudaStream_t stream) {
+  if (N < 1 || N > 64 || G < 1 || G > 256) return SB_ERR_SHAPE;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return SB_ERR_DRIVER;
+  if (g_gn_noalloc_ptr[dev] == nullptr) {
+    // once per device, with that device current: the symbol's address on THIS device
+    float* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_gn_noalloc_scratch) != cudaSuccess || p == nullptr) return SB_ERR_DRIVER;
+    g_gn_noalloc_ptr[dev] = p;
+  }
+  float* scratch = g_gn_noalloc_ptr[dev];
+  const int nsplit = sb_gn_nsplit(N, S, C);
+  const long long part_floats = (long long)N * nsplit * G * 3;
+  const long long fin_floats = (long long)N * G * 3;
+  if (part_floats + fin_floats > SB_GN_NOALLOC_SCRATCH_FLOATS) return SB_ERR_TOO_LARGE;
+  float* part = scratch;
+  float* fin = scratch + part_floats;
+  float* tail = scratch + SB_GN_NOALLOC_SCRATCH_FLOATS;  // room for mean / rstd when the caller wants neither
+  SbGnArgs a;
+  memset(&a, 0, sizeof(a));
+  a.x = x; a.y = y; a.w = w; a.b = b;
+  a.mean = mean ? mean : tail;
+  a.rstd = rstd ? rstd : tail + 256 * 64;
+  a.N = N; a.C = C; a.G = G; a.S = S; a.S_total = S;
+  a.eps = eps; a.relu = relu;
+  a.part = part;
+  a.parts[0] = part;
+  a.n_parts = 1;
+  a.nsplit = nsplit;
+  int rc = sb_gn_stats(&a, stream);
+  if (rc) return rc;
+  rc = sb_gn_stats_finalize(part, fin, N, G, nsplit, stream);
+  if (rc) return rc;
+  a.parts[0] = fin;
+  a.nsplit = 1;
+  return sb_gn_apply(&a, stream);
+}
