@@ -77,19 +77,40 @@ __global__ void __launch_bounds__(AR_THREADS) grad_allreduce_kernel(const AllRed
     const long long n4 = c1 > c0 ? (c1 - c0) / 4 : 0;
     const long long tail0 = c0 + n4 * 4;
     // phase 1 + 2 fused per element: sum over peers in rank order, scale, store to every rank
-    for (long long i = (long long)blockIdx.x * AR_THREADS + threadIdx.x; i < n4; i += (long long)gridDim.x * AR_THREADS) {
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    // four independent 16-byte lanes per thread keep enough bytes in flight to cover the NVLink latency
+    constexpr int U = 4;
+    const long long stride = (long long)gridDim.x * AR_THREADS;
+    for (long long i0 = (long long)blockIdx.x * AR_THREADS + threadIdx.x; i0 < n4; i0 += stride * U) {
+      float4 acc[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int r = 0; r < AR_MAX_RANKS; ++r) {
         if (r < p.world) {
-          const float4 v = *reinterpret_cast<const float4*>(p.bufs[r] + c0 + i * 4);
-          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          float4 v[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const long long i = i0 + u * stride;
+            v[u] = i < n4 ? __ldcs(reinterpret_cast<const float4*>(p.bufs[r] + c0 + i * 4))
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w;
+          }
         }
       }
-      acc.x *= p.scale; acc.y *= p.scale; acc.z *= p.scale; acc.w *= p.scale;
 #pragma unroll
-      for (int r = 0; r < AR_MAX_RANKS; ++r)
-        if (r < p.world) *reinterpret_cast<float4*>(p.bufs[r] + c0 + i * 4) = acc;
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < n4) {
+          float4 a = acc[u];
+          a.x *= p.scale; a.y *= p.scale; a.z *= p.scale; a.w *= p.scale;
+#pragma unroll
+          for (int r = 0; r < AR_MAX_RANKS; ++r)
+            if (r < p.world) __stcs(reinterpret_cast<float4*>(p.bufs[r] + c0 + i * 4), a);
+        }
+      }
     }
     if (blockIdx.x == 0) {
       for (long long e = tail0 + threadIdx.x; e < c1; e += AR_THREADS) {
@@ -149,7 +170,7 @@ extern "C" int sb_grad_allreduce(void* const* bufs, void* const* flags, int rank
   p.rank = rank; p.world = world; p.offset = offset; p.count = count; p.epoch = epoch; p.scale = scale;
   p.status = status;
   p.wait_ticks = (long long)(wait_seconds * 1.8e9);
-  if (ctas < 1) ctas = 32;
+  if (ctas < 1) ctas = 296;
   grad_allreduce_kernel<<<ctas, AR_THREADS, 0, stream>>>(p);
   sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;

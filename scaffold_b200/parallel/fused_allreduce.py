@@ -23,7 +23,7 @@ _lib.register("sb_grad_allreduce", [C.POINTER(_P), C.POINTER(_P), C.c_int, C.c_i
 class FusedAllReduce:
     MAX_RANKS = 8
 
-    def __init__(self, numel: int, group=None, ctas: int = 32, wait_seconds: float = 2.0):
+    def __init__(self, numel: int, group=None, ctas: int = 0, wait_seconds: float = 2.0):
         world = dist.get_world_size(group)
         if world > self.MAX_RANKS:
             raise RuntimeError(f"fused all-reduce supports up to {self.MAX_RANKS} ranks on one NVLink domain")

@@ -1,0 +1,27 @@
+"""Multi-GPU tests (skipped with fewer than two visible GPUs): child processes, one rank per GPU."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from helpers.launch import ROOT, free_port, results
+
+pytestmark = pytest.mark.gpu
+
+
+def _torchrun(script, nproc, args=(), timeout=300):
+    env = dict(os.environ)
+    env["PYTHONPATH"] = f"{ROOT}:{env.get('PYTHONPATH', '')}"
+    env["NCCL_NVLS_ENABLE"] = "0"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(free_port()), str(script), *args]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=str(ROOT))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_allreduce_matches_nccl_on_two_gpus():
+    proc = _torchrun(ROOT / "tests" / "helpers" / "rank_scripts" / "fused_allreduce_gpu.py", 2)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    assert results(proc.stdout)["equal"] == ["True"]
