@@ -434,17 +434,18 @@ extern "C" int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream) {
     const int t0 = o * p.KWS * p.KHS;  // taps ordered (kd, kh, kw), kw fastest
     const int kd = t0 / (a->ksize * a->ksize), kh = (t0 / a->ksize) % a->ksize, kw = t0 % a->ksize;
     p.tap_map[o] = 0;
-    p.tap_dd[o] = (signed char)(kd - half);
-    p.tap_dh[o] = (signed char)(kh - half);
-    p.tap_dw[o] = (signed char)(kw - half);  // shift mode: kw == 0 -> -1, the box is TW+2 wide
+    p.tap_dd[o] = (signed char)(kd - half + a->off_d);
+    p.tap_dh[o] = (signed char)(kh - half + a->off_h);
+    p.tap_dw[o] = (signed char)(kw - half + a->off_w);  // shift mode: kw == 0 -> -1, the box is TW+2 wide
   }
   p.cblks0 = a->src_c[0] / bk;
   p.cblks = cin_tot / bk;
   const int rowb = bk * 2;
   for (int s = 0; s < nsrc; ++s) {
     const long long C = a->src_ld[s];
-    long long dims[5] = {a->src_c[s], a->H, a->W, a->D, a->N};
-    long long str[5] = {1, (long long)a->W * C, C, (long long)a->H * a->W * C, (long long)a->D * a->H * a->W * C};
+    const long long iD = a->in_d ? a->in_d : a->D, iH = a->in_h ? a->in_h : a->H, iW = a->in_w ? a->in_w : a->W;
+    long long dims[5] = {a->src_c[s], iH, iW, iD, a->N};
+    long long str[5] = {1, iW * C, C, iH * iW * C, iD * iH * iW * C};
     int box[5] = {bk, p.TH + p.KHS - 1, p.TW + p.KWS - 1, p.TD, p.TN};
     rc = make_map_bf16(&p.mapA[s], a->src[s], 5, dims, str, box, rowb);
     if (rc) return rc;

@@ -44,6 +44,7 @@ struct PlaneParams {
   int N, D, H, W;
   int tiles_h, tiles_w, groups_d, tiles_co, num_jobs;
   int cblks, cblks0;
+  int off_d, off_h, off_w;  // position of output voxel 0 inside the (possibly halo'd) sources
   __nv_bfloat16* out0;
   __nv_bfloat16* out1;
   int width0, width1, ld0, ld1;
@@ -119,8 +120,8 @@ __global__ void __launch_bounds__(224, 1) conv_plane_kernel(const __grid_constan
             const uint32_t ph = (it / p.a_slots) & 1u;
             if (!mbar_wait(&a_empty[s], ph ^ 1u, abort_flag, p.status, 21)) { ok = false; break; }
             mbar_expect_tx(&a_full[s], (uint32_t)p.a_tx);
-            tma_load_5d(smem + (size_t)s * p.a_slot_bytes, &p.mapA[second], &a_full[s], c, jc.h0 - 1, jc.w0 - 1,
-                        jc.d0 - 1 + j, jc.n);
+            tma_load_5d(smem + (size_t)s * p.a_slot_bytes, &p.mapA[second], &a_full[s], c, jc.h0 - 1 + p.off_h,
+                        jc.w0 - 1 + p.off_w, jc.d0 - 1 + j + p.off_d, jc.n);
           }
         }
       }
@@ -385,8 +386,9 @@ int conv_plane_launch(const SbConvArgs* a, cudaStream_t stream) {
   p.cblks = cin_tot / bk;
   for (int s = 0; s < nsrc; ++s) {
     const long long C = a->src_ld[s];
-    long long dims[5] = {a->src_c[s], a->H, a->W, a->D, a->N};
-    long long str[5] = {1, (long long)a->W * C, C, (long long)a->H * a->W * C, (long long)a->D * a->H * a->W * C};
+    const long long iD = a->in_d ? a->in_d : a->D, iH = a->in_h ? a->in_h : a->H, iW = a->in_w ? a->in_w : a->W;
+    long long dims[5] = {a->src_c[s], iH, iW, iD, a->N};
+    long long str[5] = {1, iW * C, C, iH * iW * C, iD * iH * iW * C};
     int box[5] = {bk, PL_RH, PL_RW, 1, 1};
     rc = make_map_bf16(&p.mapA[s], a->src[s], 5, dims, str, box, rowb);
     if (rc) return rc;
@@ -408,6 +410,7 @@ int conv_plane_launch(const SbConvArgs* a, cudaStream_t stream) {
   if (p.width0 % 8 || p.width1 % 8 || p.ld0 % 8 || p.ld1 % 8) return SB_ERR_SHAPE;
   p.bias = a->bias;
   p.status = a->status;
+  p.off_d = a->off_d; p.off_h = a->off_h; p.off_w = a->off_w;
   const int grid = p.num_jobs < g_pl_sms ? p.num_jobs : g_pl_sms;
   const size_t smem = (size_t)p.a_slots * p.a_slot_bytes + (size_t)p.b_slots * p.b_slot_bytes + 1024;
 #define SB_PL_LAUNCH(TD_, KS_) conv_plane_kernel<TD_, KS_><<<grid, 224, smem, stream>>>(p)

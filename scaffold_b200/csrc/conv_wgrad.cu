@@ -41,7 +41,7 @@ struct WgradParams {
   int m_tiles, n_tiles, m_tiles0, n_tiles0;  // tiles in total / in the first source of that side
   int splits, blocks_per_split;
   int stages, stage_bytes, m_bytes, boxm_bytes, boxn_bytes, tx_bytes;
-  int m_stride;  // coordinate multiplier of the M side (always 1)
+  int m_off_d, m_off_h, m_off_w;  // added to the M-side box origin (halo'd x on the M side)
   signed char o_map[16], o_dd[16], o_dh[16], o_dw[16];
   int Mtot, Ntot, T;  // workspace extents: ws[split][T][Mtot][Ntot]
   float* ws;
@@ -113,7 +113,8 @@ __global__ void __launch_bounds__(192, 1) wgrad_kernel(const __grid_constant__ W
         uint8_t* sn = sm + p.m_bytes;
         mbar_expect_tx(&full_bar[s], (uint32_t)p.tx_bytes);
         for (int j = 0; j < p.m_boxes; ++j)
-          tma_load_5d(sm + (size_t)j * p.boxm_bytes, mm, &full_bar[s], mc0 + j * p.CBm, h0, w0, d, n);
+          tma_load_5d(sm + (size_t)j * p.boxm_bytes, mm, &full_bar[s], mc0 + j * p.CBm, h0 + p.m_off_h,
+                      w0 + p.m_off_w, d + p.m_off_d, n);
         for (int j = 0; j < p.n_boxes; ++j)
           tma_load_5d(sn + (size_t)j * p.boxn_bytes, mn, &full_bar[s], nc0 + j * p.CBn, h0 + p.o_dh[o],
                       w0 + p.o_dw[o], d + p.o_dd[o], n);
@@ -355,11 +356,26 @@ static int build_plan(const SbWgradArgs* a, Plan& pl, bool maps) {
   int rc;
   // M side maps
   auto act_map = [&](CUtensorMap* m, const void* base, int c, long long ld, int cb, int box_w) {
-    long long dims[5] = {c, a->H, a->W, a->D, a->N};
-    long long str[5] = {1, (long long)a->W * ld, ld, (long long)a->H * a->W * ld, (long long)a->D * a->H * a->W * ld};
+    // x may carry a halo (its own extents); gy always lives on the (N, D, H, W) grid
+    const bool is_x = base == a->x[0] || (a->x[1] != nullptr && base == a->x[1]);
+    const long long D = is_x && a->xin_d ? a->xin_d : a->D, H = is_x && a->xin_h ? a->xin_h : a->H,
+                    W = is_x && a->xin_w ? a->xin_w : a->W;
+    long long dims[5] = {c, H, W, D, a->N};
+    long long str[5] = {1, W * ld, ld, H * W * ld, D * H * W * ld};
     int box[5] = {cb, 8, box_w, 1, 1};
     return make_map_bf16(m, base, 5, dims, str, box, cb * 2);
   };
+  if (!convT) {
+    if (m_is_x) {
+      p.m_off_d = a->xoff_d; p.m_off_h = a->xoff_h; p.m_off_w = a->xoff_w;
+    } else {
+      for (int o = 0; o < p.n_outer; ++o) {
+        p.o_dd[o] = (signed char)(p.o_dd[o] + a->xoff_d);
+        p.o_dh[o] = (signed char)(p.o_dh[o] + a->xoff_h);
+        p.o_dw[o] = (signed char)(p.o_dw[o] + a->xoff_w);
+      }
+    }
+  }
   if (m_is_x) {
     rc = act_map(&p.mapM[0], a->x[0], a->x_c[0], a->x_ld[0], p.CBm, p.TW);
     if (rc) return rc;

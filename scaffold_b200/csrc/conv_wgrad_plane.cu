@@ -43,6 +43,8 @@ struct WgradPlaneParams {
   int splits, blocks_per_split;
   int stages, stage_bytes, g_bytes, g_tx, x_tx;
   int Mtot, Ntot;
+  int xoff_d, xoff_h, xoff_w;
+  int h_origin;  // first block row starts here (-1 when x carries an h halo, see wp_plan)
   float* ws;
   uint32_t* status;
 };
@@ -106,12 +108,12 @@ __global__ void __launch_bounds__(192, 1) wgrad_plane_kernel(const __grid_consta
         const int ht = b % p.tiles_h; b /= p.tiles_h;
         const int d = b % p.D; b /= p.D;
         const int n = b;
-        const int h0 = ht * 8, w0 = wt * p.TW;
+        const int h0 = ht * 8 + p.h_origin, w0 = wt * p.TW;
         uint8_t* sg = smem + (size_t)s * p.stage_bytes;
         uint8_t* sx = sg + p.g_bytes;
         mbar_expect_tx(&full_bar[s], (uint32_t)(p.g_tx + p.x_tx));
         tma_load_5d(sg, &p.mapG, &full_bar[s], mt * p.CM, h0, w0, d, n);
-        tma_load_5d(sx, mx, &full_bar[s], nc0, h0, w0 - 1, d + kd - 1, n);
+        tma_load_5d(sx, mx, &full_bar[s], nc0, h0 + p.xoff_h, w0 - 1 + p.xoff_w, d + kd - 1 + p.xoff_d, n);
       }
     }
   } else if (warp == 1) {
@@ -239,7 +241,10 @@ static int wp_plan(const SbWgradArgs* a, WgradPlaneParams& p) {
   p.N = a->N; p.D = a->D; p.H = a->H; p.W = a->W;
   p.TW = a->W >= 16 ? 16 : 8;
   p.KV = 8 * p.TW;
-  p.tiles_h = cdiv_wp(a->H, 8);
+  // The h-shifted copy of gy never covers output row 0; that is harmless when x[-1] is zero padding, but
+  // with an h halo in x the row is real data, so the blocks then start one row early (gy row -1 reads zero).
+  p.h_origin = a->xoff_h != 0 ? -1 : 0;
+  p.tiles_h = cdiv_wp(a->H - p.h_origin, 8);
   p.tiles_w = cdiv_wp(a->W, p.TW);
   p.nblocks = a->N * a->D * p.tiles_h * p.tiles_w;
   p.m_tiles = gc / p.CM;
@@ -280,18 +285,21 @@ int wgrad_plane_launch(const SbWgradArgs* a, cudaStream_t stream, int* splits_ou
   if (st > WP_MAX_STAGES) st = WP_MAX_STAGES;
   if (st < 2) return -1;
   p.stages = st;
-  auto act_map = [&](CUtensorMap* m, const void* base, int c, long long ld, int cb, int box_w) {
-    long long dims[5] = {c, a->H, a->W, a->D, a->N};
-    long long str[5] = {1, (long long)a->W * ld, ld, (long long)a->H * a->W * ld, (long long)a->D * a->H * a->W * ld};
+  auto act_map = [&](CUtensorMap* m, const void* base, int c, long long ld, int cb, int box_w, bool is_x) {
+    const long long D = is_x && a->xin_d ? a->xin_d : a->D, H = is_x && a->xin_h ? a->xin_h : a->H,
+                    W = is_x && a->xin_w ? a->xin_w : a->W;
+    long long dims[5] = {c, H, W, D, a->N};
+    long long str[5] = {1, W * ld, ld, H * W * ld, D * H * W * ld};
     int box[5] = {cb, WP_RH, box_w, 1, 1};
     return make_map_bf16(m, base, 5, dims, str, box, cb * 2);
   };
-  rc = act_map(&p.mapG, a->gy, a->gy_c, a->gy_ld, p.CM, p.TW);
+  p.xoff_d = a->xoff_d; p.xoff_h = a->xoff_h; p.xoff_w = a->xoff_w;
+  rc = act_map(&p.mapG, a->gy, a->gy_c, a->gy_ld, p.CM, p.TW, false);
   if (rc) return rc;
-  rc = act_map(&p.mapX[0], a->x[0], a->x_c[0], a->x_ld[0], p.CN, p.TW + 2);
+  rc = act_map(&p.mapX[0], a->x[0], a->x_c[0], a->x_ld[0], p.CN, p.TW + 2, true);
   if (rc) return rc;
   if (a->x_c[1] > 0) {
-    rc = act_map(&p.mapX[1], a->x[1], a->x_c[1], a->x_ld[1], p.CN, p.TW + 2);
+    rc = act_map(&p.mapX[1], a->x[1], a->x_c[1], a->x_ld[1], p.CN, p.TW + 2, true);
     if (rc) return rc;
   } else {
     p.mapX[1] = p.mapX[0];

@@ -35,7 +35,12 @@ typedef struct {
   int dst_ld[2];  // channel stride of each destination
   const float* bias;  // optional, added to destination 0 columns
   uint32_t* status;   // optional 4-word status block
-  int force_plain;    // tests: disable the w-shift reuse path
+  int force_plain;    // tests: 0 automatic, 1..3 select a variant of the generic kernel
+  // Spatially sharded volumes: the sources may carry a halo. in_* are the sources' spatial
+  // extents (0 = same as D/H/W) and off_* the position of output voxel 0 inside them, so
+  // input coordinate = output coordinate + tap - k/2 + off (negative offsets read zeros).
+  int in_d, in_h, in_w;
+  int off_d, off_h, off_w;
 } SbConvArgs;
 
 // k=2,s=2 transposed convolution. Forward: src [N,D,H,W,cin] -> dst
@@ -71,6 +76,9 @@ typedef struct {
   int accumulate;     // add into dw instead of overwriting
   uint32_t* status;
   int splits;         // 0: choose
+  // halo'd x (see SbConvArgs): extents of x (0 = same as the gy grid) and offset of voxel 0 in it
+  int xin_d, xin_h, xin_w;
+  int xoff_d, xoff_h, xoff_w;
 } SbWgradArgs;
 
 // GroupNorm (+ReLU), channels-last bf16. `parts` lists the partial-statistics

@@ -44,6 +44,8 @@ class SbConvArgs(C.Structure):
         ("bias", C.c_void_p),
         ("status", C.c_void_p),
         ("force_plain", C.c_int),
+        ("in_d", C.c_int), ("in_h", C.c_int), ("in_w", C.c_int),
+        ("off_d", C.c_int), ("off_h", C.c_int), ("off_w", C.c_int),
     ]
 
 
@@ -77,6 +79,8 @@ class SbWgradArgs(C.Structure):
         ("accumulate", C.c_int),
         ("status", C.c_void_p),
         ("splits", C.c_int),
+        ("xin_d", C.c_int), ("xin_h", C.c_int), ("xin_w", C.c_int),
+        ("xoff_d", C.c_int), ("xoff_h", C.c_int), ("xoff_w", C.c_int),
     ]
 
 

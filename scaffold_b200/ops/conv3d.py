@@ -65,8 +65,11 @@ class _ConvSameFn(torch.autograd.Function):
     """k in {1,3} stride-1 'same' conv over voxel-major bf16 sources."""
 
     @staticmethod
-    def forward(ctx, weight, bias, mod, n_src, *xs):
+    def forward(ctx, weight, bias, mod, in_off, *xs):
         ks = weight.shape[2]
+        in_off = tuple(int(v) for v in in_off)
+        in_dims = tuple(xs[0].shape[1:4])
+        out_dims = tuple(d - 2 * o for d, o in zip(in_dims, in_off))
         src_c = [x.shape[4] for x in xs]
         real_c = mod._real_in_channels(src_c)
         wf = mod._cache.get(weight, f"fwd{src_c}", lambda w: ck.pack_weight_fwd(_pad_in_channels(w, src_c, real_c)))
@@ -74,8 +77,9 @@ class _ConvSameFn(torch.autograd.Function):
         bpad = None
         if bias is not None:
             bpad = mod._cache_b.get(bias, "b", lambda b: F.pad(b, (0, cout_pad - b.shape[0])).contiguous())
-        (y,) = ck.conv_same(list(xs), wf, ks, [cout_pad], bias=bpad)
+        (y,) = ck.conv_same(list(xs), wf, ks, [cout_pad], bias=bpad, out_dims=out_dims, in_off=in_off)
         ctx.mod = mod
+        ctx.in_off, ctx.in_dims = in_off, in_dims
         ctx.src_c, ctx.real_c = src_c, real_c
         ctx.has_bias = bias is not None
         ctx.save_for_backward(weight, *xs)
@@ -95,7 +99,8 @@ class _ConvSameFn(torch.autograd.Function):
                 # pack_weight_dgrad pads Cout to a multiple of 16, which is gy's channel count
                 return ck.pack_weight_dgrad(_pad_in_channels(w, src_c, real_c))
             wd = mod._cache.get(weight, f"dgrad{src_c}", pack)
-            outs = ck.conv_same([gy], wd, ks, src_c)
+            # a halo'd input gets a halo'd gradient: output grid = input extents, gy read at -offset
+            outs = ck.conv_same([gy], wd, ks, src_c, out_dims=ctx.in_dims, in_off=[-o for o in ctx.in_off])
             for i, o in enumerate(outs):
                 if need_gx[i]:
                     gxs[i] = o
@@ -103,11 +108,11 @@ class _ConvSameFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             gw = torch.empty_like(weight, dtype=torch.float32)
             if list(src_c) == list(real_c):
-                ck.conv_wgrad(gy, list(xs), ks, gw)
+                ck.conv_wgrad(gy, list(xs), ks, gw, x_off=ctx.in_off)
             else:
                 # channel-padded sources (the 3-channel stem): gradient over padded Cin, then slice
                 gwp = torch.empty((weight.shape[0], sum(src_c), ks, ks, ks), dtype=torch.float32, device=gy.device)
-                ck.conv_wgrad(gy, list(xs), ks, gwp)
+                ck.conv_wgrad(gy, list(xs), ks, gwp, x_off=ctx.in_off)
                 parts, o = [], 0
                 for sc, rc in zip(src_c, real_c):
                     parts.append(gwp[:, o:o + rc])
@@ -149,8 +154,7 @@ class Conv3d(nn.Conv3d):
             if not self._kernel_ok():
                 raise NotImplementedError(
                     f"sm_100a conv kernels cover k in (1,3), stride 1, 'same' zero padding; got {self}")
-            vms = [to_vm(t, pad16=True) for t in xs]
-            y = _ConvSameFn.apply(self.weight, self.bias, self, len(vms), *vms)
+            y = self._cuda_forward(xs)
             out = from_vm(y)
             return out if y.shape[4] == self.out_channels else out[:, : self.out_channels]
         xin = xs[0] if len(xs) == 1 else torch.cat([t.to(xs[0].dtype) for t in xs], dim=1)
@@ -162,11 +166,21 @@ class Conv3d(nn.Conv3d):
                             self.dilation, self.groups)
         return super().forward(xin)
 
+    def _cuda_forward(self, xs) -> torch.Tensor:
+        """Voxel-major output of the kernel path; on a sharded volume the sources first receive their halo."""
+        sp = self._spatial
+        off = (0, 0, 0)
+        if sp is not None and sp.size > 1 and self.kernel_size[0] > 1:
+            halo = self.kernel_size[0] // 2
+            xs = [sp.halo_pad(t, halo) for t in xs]
+            off = tuple(halo if d in sp.dims else 0 for d in (2, 3, 4))
+        vms = [to_vm(t, pad16=True) for t in xs]
+        return _ConvSameFn.apply(self.weight, self.bias, self, off, *vms)
+
     def forward_padded(self, x) -> torch.Tensor:
         """CUDA path only: voxel-major output with the channel axis padded to a multiple of 16."""
         xs = [x] if isinstance(x, torch.Tensor) else list(x)
-        vms = [to_vm(t, pad16=True) for t in xs]
-        return _ConvSameFn.apply(self.weight, self.bias, self, len(vms), *vms)
+        return self._cuda_forward(xs)
 
 
 class _ConvTFn(torch.autograd.Function):

@@ -71,15 +71,19 @@ def _chk_act(t: torch.Tensor) -> None:
 
 def conv_same(srcs: Sequence[torch.Tensor], wpack: torch.Tensor, ksize: int,
               dst_channels: Sequence[int], bias: Optional[torch.Tensor] = None,
-              force_plain: bool = False, out: Optional[Sequence[torch.Tensor]] = None):
+              force_plain: bool = False, out: Optional[Sequence[torch.Tensor]] = None,
+              out_dims: Optional[Sequence[int]] = None, in_off: Sequence[int] = (0, 0, 0)):
     """Stride-1 'same' convolution of the channel concatenation of ``srcs``.
 
     Returns a list of outputs, one per entry of ``dst_channels`` (the output
-    channels are split in that order).
+    channels are split in that order). ``out_dims`` (D, H, W) and ``in_off`` describe
+    halo'd sources of a sharded volume: output voxel 0 sits at ``in_off`` inside the
+    sources (negative offsets read zeros, which is how backward-data grows a halo).
     """
     for s in srcs:
         _chk_act(s)
-    n, d, h, w = srcs[0].shape[:4]
+    n = srcs[0].shape[0]
+    d, h, w = out_dims if out_dims is not None else srcs[0].shape[1:4]
     a = _lib.SbConvArgs()
     for i in range(2):
         if i < len(srcs):
@@ -91,6 +95,8 @@ def conv_same(srcs: Sequence[torch.Tensor], wpack: torch.Tensor, ksize: int,
             a.src_c[i] = 0
             a.src_ld[i] = 0
     a.N, a.D, a.H, a.W = n, d, h, w
+    a.in_d, a.in_h, a.in_w = srcs[0].shape[1:4]
+    a.off_d, a.off_h, a.off_w = (int(v) for v in in_off)
     a.ksize = ksize
     a.wpack = wpack.data_ptr()
     a.cout_pad = wpack.shape[1]
@@ -161,7 +167,7 @@ def _workspace(device, elems: int) -> torch.Tensor:
 
 
 def conv_wgrad(gy: torch.Tensor, xs: Sequence[torch.Tensor], ksize: int, dw: torch.Tensor,
-               accumulate: bool = False, splits: int = 0) -> torch.Tensor:
+               accumulate: bool = False, splits: int = 0, x_off: Sequence[int] = (0, 0, 0)) -> torch.Tensor:
     """Weight gradient into ``dw`` (fp32, parameter layout).
 
     ksize 1/3: ``dw`` is [Cout, Cin, k,k,k]; ``gy`` and ``xs`` share the voxel grid.
@@ -171,7 +177,12 @@ def conv_wgrad(gy: torch.Tensor, xs: Sequence[torch.Tensor], ksize: int, dw: tor
     for x in xs:
         _chk_act(x)
     n, d, h, w = xs[0].shape[:4]
+    if ksize != 2:
+        d, h, w = gy.shape[1:4]  # x may carry a halo; the voxel grid is gy's
     a = _lib.SbWgradArgs()
+    if ksize != 2:
+        a.xin_d, a.xin_h, a.xin_w = xs[0].shape[1:4]
+        a.xoff_d, a.xoff_h, a.xoff_w = (int(v) for v in x_off)
     a.gy, a.gy_c, a.gy_ld = gy.data_ptr(), gy.shape[4], gy.shape[4]
     for i in range(2):
         if i < len(xs):

@@ -212,3 +212,37 @@ def test_negative_control_unflipped_dgrad_differs():
     torch.cuda.synchronize()
     _lib.check_status()
     assert not torch.equal(ncdhw(gx), ref)
+
+
+@pytest.mark.parametrize("dim,mode", [(0, 0), (1, 0), (2, 0), (0, 1), (2, 2)], ids=lambda v: str(v))
+def test_halo_input_conv_fwd_dgrad_wgrad_bitwise(dim, mode):
+    """A shard with a one-voxel halo on one dim: forward, backward-data and weight gradient against autograd."""
+    _lib, ck = _ck()
+    g = torch.Generator(device="cuda").manual_seed(21 + dim)
+    cin, cout = 64, 64
+    local = [4, 16, 32]
+    in_dims = list(local)
+    in_dims[dim] += 2
+    x_h = tri((1, cin, *in_dims), g, density=0.5)
+    wt = tri((cout, cin, 3, 3, 3), g, density=0.5)
+    gy = tri((1, cout, *local), g, density=0.5)
+    pad = [1, 1, 1]
+    pad[dim] = 0
+    xr = x_h.double().requires_grad_(True)
+    wr = wt.double().requires_grad_(True)
+    ref = F.conv3d(xr, wr, padding=tuple(pad))
+    ref.backward(gy.double())
+    off = [0, 0, 0]
+    off[dim] = 1
+    (y,) = ck.conv_same([ndhwc(x_h)], ck.pack_weight_fwd(wt), 3, [cout], force_plain=mode, out_dims=local, in_off=off)
+    torch.cuda.synchronize(); _lib.check_status()
+    assert torch.equal(ncdhw(y), ref.detach().round().to(torch.bfloat16).double())
+    # backward-data grows the halo: output grid = halo'd extents, gy read at a negative offset
+    (gx,) = ck.conv_same([ndhwc(gy)], ck.pack_weight_dgrad(wt), 3, [cin], force_plain=mode, out_dims=in_dims,
+                         in_off=[-o for o in off])
+    torch.cuda.synchronize(); _lib.check_status()
+    assert torch.equal(ncdhw(gx), xr.grad.round().to(torch.bfloat16).double())
+    dw = torch.full((cout, cin, 3, 3, 3), float("nan"), device="cuda")
+    ck.conv_wgrad(ndhwc(gy), [ndhwc(x_h)], 3, dw, splits=0 if mode == 0 else -1, x_off=off)
+    torch.cuda.synchronize(); _lib.check_status()
+    assert torch.equal(dw.double(), wr.grad.round())

@@ -25,3 +25,14 @@ def test_fused_allreduce_matches_nccl_on_two_gpus():
     proc = _torchrun(ROOT / "tests" / "helpers" / "rank_scripts" / "fused_allreduce_gpu.py", 2)
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
     assert results(proc.stdout)["equal"] == ["True"]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("split_dim", [2, 4])
+def test_two_spatial_shards_match_the_whole_volume_on_gpu(split_dim):
+    proc = _torchrun(ROOT / "tests" / "helpers" / "rank_scripts" / "spatial_gpu.py", 2, [str(split_dim)])
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
+    res = results(proc.stdout)
+    a, b = (float(v) for v in res["loss"][0].split())
+    assert abs(a - b) <= 2e-3 * max(1.0, abs(b)), res
+    assert float(res["grad_rel"][0]) < 0.08, res
