@@ -408,6 +408,7 @@ extern "C" int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream) {
     const int prc = conv_plane_launch(a, stream);
     if (prc >= 0) return prc;
   }
+  if (a->halo_land[0][0] || a->halo_land[0][1] || a->slab_out[0]) return SB_ERR_SHAPE;  // plane-walk kernel only
   int rc = device_setup();
   if (rc) return rc;
   IgemmParams p;

@@ -45,6 +45,15 @@ struct PlaneParams {
   int tiles_h, tiles_w, groups_d, tiles_co, num_jobs;
   int cblks, cblks0;
   int off_d, off_h, off_w;  // position of output voxel 0 inside the (possibly halo'd) sources
+  // fused depth halo: landing slabs of the neighbours' boundary planes, guarded by flag words
+  CUtensorMap mapHalo[4];  // [source * 2 + face]
+  int halo_has[2], in_D;
+  const uint32_t* halo_flag[2];
+  uint32_t halo_epoch;
+  long long halo_wait_ticks;
+  // backward-data with halo: output planes 0 and D-1 go to slabs
+  __nv_bfloat16* slab_out[2];
+  int slab_ld, slab_mode;
   __nv_bfloat16* out0;
   __nv_bfloat16* out1;
   int width0, width1, ld0, ld1;
@@ -110,6 +119,7 @@ __global__ void __launch_bounds__(224, 1) conv_plane_kernel(const __grid_constan
       tma_prefetch_desc(&p.mapA[1]);
       uint32_t it = 0;
       bool ok = true;
+      bool halo_ready[2] = {false, false};
       for (int job = blockIdx.x; job < p.num_jobs && ok; job += gridDim.x) {
         const JobCoord jc = decode_job(p, job);
         for (int cb = 0; cb < p.cblks && ok; ++cb) {
@@ -119,9 +129,38 @@ __global__ void __launch_bounds__(224, 1) conv_plane_kernel(const __grid_constan
             const int s = it % p.a_slots;
             const uint32_t ph = (it / p.a_slots) & 1u;
             if (!mbar_wait(&a_empty[s], ph ^ 1u, abort_flag, p.status, 21)) { ok = false; break; }
-            mbar_expect_tx(&a_full[s], (uint32_t)p.a_tx);
-            tma_load_5d(smem + (size_t)s * p.a_slot_bytes, &p.mapA[second], &a_full[s], c, jc.h0 - 1 + p.off_h,
-                        jc.w0 - 1 + p.off_w, jc.d0 - 1 + j + p.off_d, jc.n);
+            const int dz = jc.d0 - 1 + j + p.off_d;
+            const int face = dz < 0 ? 0 : (dz >= p.in_D ? 1 : -1);
+            if (face >= 0 && p.halo_has[face]) {
+              // a neighbour's boundary plane: wait (bounded) until its push landed, then read it locally
+              if (!halo_ready[face]) {
+                if (p.halo_flag[face] != nullptr) {
+                  const long long t0 = clock64();
+                  uint32_t v;
+                  while (true) {
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.halo_flag[face]) : "memory");
+                    if ((int)(v - p.halo_epoch) >= 0) break;
+                    if (*abort_flag || clock64() - t0 > p.halo_wait_ticks) {
+                      *abort_flag = 1u;
+                      report(p.status, ST_FLAG_TIMEOUT, 27, blockIdx.x, face);
+                      ok = false;
+                      break;
+                    }
+                    __nanosleep(32);
+                  }
+                  if (!ok) break;
+                  asm volatile("fence.proxy.async;" ::: "memory");
+                }
+                halo_ready[face] = true;
+              }
+              mbar_expect_tx(&a_full[s], (uint32_t)p.a_tx);
+              tma_load_5d(smem + (size_t)s * p.a_slot_bytes, &p.mapHalo[second * 2 + face], &a_full[s], c,
+                          jc.h0 - 1 + p.off_h, jc.w0 - 1 + p.off_w, 0, jc.n);
+            } else {
+              mbar_expect_tx(&a_full[s], (uint32_t)p.a_tx);
+              tma_load_5d(smem + (size_t)s * p.a_slot_bytes, &p.mapA[second], &a_full[s], c, jc.h0 - 1 + p.off_h,
+                          jc.w0 - 1 + p.off_w, dz, jc.n);
+            }
           }
         }
       }
@@ -247,7 +286,15 @@ __global__ void __launch_bounds__(224, 1) conv_plane_kernel(const __grid_constan
       for (int t = 0; t < TD; ++t) {
         const int d = jc.d0 + t;
         const bool valid = h < p.H && w < p.W && d < p.D;
-        const long long vox = (((long long)jc.n * p.D + d) * p.H + h) * p.W + w;
+        long long vox = (((long long)jc.n * p.D + d) * p.H + h) * p.W + w;
+        __nv_bfloat16* slab = nullptr;
+        if (p.slab_mode) {
+          // output grid = D+2 planes: the two outermost are the halo's gradient and live in slabs
+          if (d == 0) slab = p.slab_out[0];
+          else if (d == p.D - 1) slab = p.slab_out[1];
+          if (slab) vox = ((long long)jc.n * p.H + h) * p.W + w;
+          else vox = (((long long)jc.n * (p.D - 2) + (d - 1)) * p.H + h) * p.W + w;
+        }
         const uint32_t acc_i = buf * TD + t;
         const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + acc_i * p.BN;
         const int nchunk = (p.BN + 31) / 32;
@@ -272,7 +319,9 @@ __global__ void __launch_bounds__(224, 1) conv_plane_kernel(const __grid_constan
 #pragma unroll
               for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[g * 8 + e]);
               __nv_bfloat16* dst = nullptr;
-              if (col < p.width0) {
+              if (slab) {
+                if (col < p.width0 + p.width1) dst = slab + vox * p.slab_ld + col;
+              } else if (col < p.width0) {
                 dst = p.out0 + vox * p.ld0 + col;
                 if (p.bias) {
 #pragma unroll
@@ -411,6 +460,32 @@ int conv_plane_launch(const SbConvArgs* a, cudaStream_t stream) {
   p.bias = a->bias;
   p.status = a->status;
   p.off_d = a->off_d; p.off_h = a->off_h; p.off_w = a->off_w;
+  p.in_D = a->in_d ? a->in_d : a->D;
+  for (int f = 0; f < 2; ++f) {
+    p.halo_has[f] = a->halo_land[0][f] != nullptr ? 1 : 0;
+    p.halo_flag[f] = a->halo_flag[f];
+    for (int s = 0; s < 2; ++s) {
+      const int idx = s * 2 + f;
+      if (s < nsrc && a->halo_land[s][f] != nullptr) {
+        const long long C = a->src_c[s];
+        const long long iH = a->in_h ? a->in_h : a->H, iW = a->in_w ? a->in_w : a->W;
+        long long dims[5] = {C, iH, iW, 1, a->N};
+        long long str[5] = {1, iW * C, C, iH * iW * C, iH * iW * C};
+        int box[5] = {bk, PL_RH, PL_RW, 1, 1};
+        rc = make_map_bf16(&p.mapHalo[idx], a->halo_land[s][f], 5, dims, str, box, rowb);
+        if (rc) return rc;
+      } else {
+        p.mapHalo[idx] = p.mapA[0];
+      }
+    }
+  }
+  p.halo_epoch = a->halo_epoch;
+  p.halo_wait_ticks = (long long)((a->halo_wait_s > 0 ? a->halo_wait_s : 2.0) * 1.8e9);
+  p.slab_mode = a->slab_out[0] != nullptr ? 1 : 0;
+  p.slab_out[0] = (__nv_bfloat16*)a->slab_out[0];
+  p.slab_out[1] = (__nv_bfloat16*)a->slab_out[1];
+  p.slab_ld = a->slab_ld;
+  if (p.slab_mode && (p.slab_ld % 8 != 0 || a->D < 3)) return SB_ERR_SHAPE;
   const int grid = p.num_jobs < g_pl_sms ? p.num_jobs : g_pl_sms;
   const size_t smem = (size_t)p.a_slots * p.a_slot_bytes + (size_t)p.b_slots * p.b_slot_bytes + 1024;
 #define SB_PL_LAUNCH(TD_, KS_) conv_plane_kernel<TD_, KS_><<<grid, 224, smem, stream>>>(p)

@@ -472,6 +472,7 @@ extern "C" int sb_conv_wgrad(const SbWgradArgs* a, cudaStream_t stream) {
       return run_reduce(a, r, stream);
     }
   }
+  if (a->xhalo[0][0] || a->xhalo[0][1]) return SB_ERR_SHAPE;  // slab halos: plane kernel only
   rc = wg_setup();
   if (rc) return rc;
   Plan pl;

@@ -44,6 +44,8 @@ struct WgradPlaneParams {
   int stages, stage_bytes, g_bytes, g_tx, x_tx;
   int Mtot, Ntot;
   int xoff_d, xoff_h, xoff_w;
+  CUtensorMap mapXh[4];  // depth-halo slabs of x: [source * 2 + face]
+  int xh_has[2], xin_D;
   int h_origin;  // first block row starts here (-1 when x carries an h halo, see wp_plan)
   float* ws;
   uint32_t* status;
@@ -113,7 +115,12 @@ __global__ void __launch_bounds__(192, 1) wgrad_plane_kernel(const __grid_consta
         uint8_t* sx = sg + p.g_bytes;
         mbar_expect_tx(&full_bar[s], (uint32_t)(p.g_tx + p.x_tx));
         tma_load_5d(sg, &p.mapG, &full_bar[s], mt * p.CM, h0, w0, d, n);
-        tma_load_5d(sx, mx, &full_bar[s], nc0, h0 + p.xoff_h, w0 - 1 + p.xoff_w, d + kd - 1 + p.xoff_d, n);
+        const int dz = d + kd - 1 + p.xoff_d;
+        const int face = dz < 0 ? 0 : (dz >= p.xin_D ? 1 : -1);
+        if (face >= 0 && p.xh_has[face])
+          tma_load_5d(sx, &p.mapXh[nsrc * 2 + face], &full_bar[s], nc0, h0 + p.xoff_h, w0 - 1 + p.xoff_w, 0, n);
+        else
+          tma_load_5d(sx, mx, &full_bar[s], nc0, h0 + p.xoff_h, w0 - 1 + p.xoff_w, dz, n);
       }
     }
   } else if (warp == 1) {
@@ -294,6 +301,8 @@ int wgrad_plane_launch(const SbWgradArgs* a, cudaStream_t stream, int* splits_ou
     return make_map_bf16(m, base, 5, dims, str, box, cb * 2);
   };
   p.xoff_d = a->xoff_d; p.xoff_h = a->xoff_h; p.xoff_w = a->xoff_w;
+  p.xin_D = a->xin_d ? a->xin_d : a->D;
+  for (int f = 0; f < 2; ++f) p.xh_has[f] = a->xhalo[0][f] != nullptr ? 1 : 0;
   rc = act_map(&p.mapG, a->gy, a->gy_c, a->gy_ld, p.CM, p.TW, false);
   if (rc) return rc;
   rc = act_map(&p.mapX[0], a->x[0], a->x_c[0], a->x_ld[0], p.CN, p.TW + 2, true);
@@ -304,6 +313,20 @@ int wgrad_plane_launch(const SbWgradArgs* a, cudaStream_t stream, int* splits_ou
   } else {
     p.mapX[1] = p.mapX[0];
   }
+  for (int s = 0; s < 2; ++s)
+    for (int f = 0; f < 2; ++f) {
+      if (a->x_c[s] > 0 && a->xhalo[s][f] != nullptr) {
+        const long long C = a->x_c[s];
+        const long long H = a->xin_h ? a->xin_h : a->H, W = a->xin_w ? a->xin_w : a->W;
+        long long dims[5] = {C, H, W, 1, a->N};
+        long long str[5] = {1, W * C, C, H * W * C, H * W * C};
+        int box[5] = {p.CN, WP_RH, p.TW + 2, 1, 1};
+        rc = make_map_bf16(&p.mapXh[s * 2 + f], a->xhalo[s][f], 5, dims, str, box, p.CN * 2);
+        if (rc) return rc;
+      } else {
+        p.mapXh[s * 2 + f] = p.mapX[0];
+      }
+    }
   p.ws = a->workspace;
   p.status = a->status;
   const int grid = 3 * p.m_tiles * p.n_tiles * p.splits;

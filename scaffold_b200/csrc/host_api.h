@@ -41,6 +41,17 @@ typedef struct {
   // input coordinate = output coordinate + tap - k/2 + off (negative offsets read zeros).
   int in_d, in_h, in_w;
   int off_d, off_h, off_w;
+  // Depth-sharded volume with the halo fused into the kernel (plane-walk kernel only): the
+  // sources hold this rank's planes only; plane -1 / plane in_d are read from landing slabs
+  // [N,1,H,W,src_c] that the neighbours fill over NVLink, after the flag word reached the epoch.
+  const void* halo_land[2][2];   // [source][0 = low face, 1 = high face], null = volume boundary
+  const unsigned* halo_flag[2];  // per face; null = data already in place (no wait)
+  unsigned halo_epoch;
+  double halo_wait_s;
+  // Backward-data of such a convolution: the output grid has D+2 planes; plane 0 and plane D+1
+  // (gradient of the halo) go to slab_out[0] / slab_out[1] ([N,1,H,W,slab_ld]), the rest to dst.
+  void* slab_out[2];
+  int slab_ld;
 } SbConvArgs;
 
 // k=2,s=2 transposed convolution. Forward: src [N,D,H,W,cin] -> dst
@@ -79,6 +90,8 @@ typedef struct {
   // halo'd x (see SbConvArgs): extents of x (0 = same as the gy grid) and offset of voxel 0 in it
   int xin_d, xin_h, xin_w;
   int xoff_d, xoff_h, xoff_w;
+  // depth halo of x kept as separate slabs [N,1,H,W,x_c[s]] (see SbConvArgs.halo_land); null = zeros
+  const void* xhalo[2][2];
 } SbWgradArgs;
 
 // GroupNorm (+ReLU), channels-last bf16. `parts` lists the partial-statistics

@@ -46,6 +46,12 @@ class SbConvArgs(C.Structure):
         ("force_plain", C.c_int),
         ("in_d", C.c_int), ("in_h", C.c_int), ("in_w", C.c_int),
         ("off_d", C.c_int), ("off_h", C.c_int), ("off_w", C.c_int),
+        ("halo_land", (C.c_void_p * 2) * 2),
+        ("halo_flag", C.c_void_p * 2),
+        ("halo_epoch", C.c_uint),
+        ("halo_wait_s", C.c_double),
+        ("slab_out", C.c_void_p * 2),
+        ("slab_ld", C.c_int),
     ]
 
 
@@ -81,6 +87,7 @@ class SbWgradArgs(C.Structure):
         ("splits", C.c_int),
         ("xin_d", C.c_int), ("xin_h", C.c_int), ("xin_w", C.c_int),
         ("xoff_d", C.c_int), ("xoff_h", C.c_int), ("xoff_w", C.c_int),
+        ("xhalo", (C.c_void_p * 2) * 2),
     ]
 
 
@@ -171,6 +178,8 @@ SITES = {
     24: "plane conv: MMA waiting for an activation plane",
     25: "plane conv: MMA waiting for a free accumulator",
     26: "plane conv: epilogue waiting for the accumulators",
+    27: "plane conv: waiting for a neighbour's halo plane",
+    51: "halo accumulate: waiting for a neighbour's gradient slab",
     31: "plane wgrad: producer waiting for a free stage",
     32: "plane wgrad: MMA waiting for operands",
     33: "plane wgrad: epilogue waiting for the accumulators",

@@ -123,6 +123,48 @@ class _ConvSameFn(torch.autograd.Function):
         return (gw, gb, None, None, *gxs)
 
 
+class _ConvHaloFn(torch.autograd.Function):
+    """3x3x3 conv on a depth-sharded volume with the halo fused into the kernels (no padded copy)."""
+
+    @staticmethod
+    def forward(ctx, weight, bias, mod, chan, *xs):
+        src_c = [x.shape[4] for x in xs]
+        wf = mod._cache.get(weight, f"fwd{src_c}", ck.pack_weight_fwd)
+        cout_pad = wf.shape[1]
+        landing = chan.exchange([x[:, 0] for x in xs], [x[:, -1] for x in xs])
+        (y,) = ck.conv_same(list(xs), wf, 3, [cout_pad], halo=landing)
+        ctx.halo_saved = landing.clone()  # the arena slot is recycled; backward needs the planes again
+        ctx.mod, ctx.chan, ctx.src_c = mod, chan, src_c
+        ctx.save_for_backward(weight, *xs)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        weight, *xs = ctx.saved_tensors
+        mod, chan, src_c = ctx.mod, ctx.chan, ctx.src_c
+        gy = gy.contiguous()
+        n, d, h, w, _ = gy.shape
+        gxs: List[Optional[torch.Tensor]] = [None] * len(xs)
+        if any(ctx.needs_input_grad[4 + i] for i in range(len(xs))):
+            wd = mod._cache.get(weight, f"dgrad{src_c}", ck.pack_weight_dgrad)
+            ctot = sum(src_c)
+            slabs = [torch.empty((n, 1, h, w, ctot), dtype=torch.bfloat16, device=gy.device) for _ in range(2)]
+            outs = ck.conv_same([gy], wd, 3, src_c, out_dims=(d + 2, h, w), in_off=(-1, 0, 0), slabs=slabs,
+                                out=[torch.empty((n, d, h, w, c), dtype=torch.bfloat16, device=gy.device)
+                                     for c in src_c])
+            # the halo's gradient goes home: my low slab is the low neighbour's last plane, and vice versa
+            landing = chan.exchange([slabs[0][:, 0]], [slabs[1][:, 0]])
+            chan.accumulate(outs, landing, ctot)
+            for i, o in enumerate(outs):
+                if ctx.needs_input_grad[4 + i]:
+                    gxs[i] = o
+        gw = None
+        if ctx.needs_input_grad[0]:
+            gw = torch.empty_like(weight, dtype=torch.float32)
+            ck.conv_wgrad(gy, list(xs), 3, gw, x_halo=ctx.halo_saved)
+        return (gw, None, None, None, *gxs)
+
+
 class Conv3d(nn.Conv3d):
     """3-D convolution; drop-in for ``nn.Conv3d`` (k=1 or k=3 'same', stride 1 on the CUDA path)."""
 
@@ -170,6 +212,13 @@ class Conv3d(nn.Conv3d):
         """Voxel-major output of the kernel path; on a sharded volume the sources first receive their halo."""
         sp = self._spatial
         off = (0, 0, 0)
+        if sp is not None and sp.size > 1 and self.kernel_size[0] == 3 and sp.halo_channel is not None:
+            vms = [to_vm(t, pad16=True) for t in xs]
+            d, h, w = vms[0].shape[1:4]
+            real = self._real_in_channels([v.shape[4] for v in vms])
+            if h >= 8 and w >= 16 and d >= 2 and self.bias is None and real == [v.shape[4] for v in vms] \
+                    and self.out_channels % 16 == 0:
+                return _ConvHaloFn.apply(self.weight, self.bias, self, sp.halo_channel, *vms)
         if sp is not None and sp.size > 1 and self.kernel_size[0] > 1:
             halo = self.kernel_size[0] // 2
             xs = [sp.halo_pad(t, halo) for t in xs]

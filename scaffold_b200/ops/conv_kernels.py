@@ -72,7 +72,8 @@ def _chk_act(t: torch.Tensor) -> None:
 def conv_same(srcs: Sequence[torch.Tensor], wpack: torch.Tensor, ksize: int,
               dst_channels: Sequence[int], bias: Optional[torch.Tensor] = None,
               force_plain: bool = False, out: Optional[Sequence[torch.Tensor]] = None,
-              out_dims: Optional[Sequence[int]] = None, in_off: Sequence[int] = (0, 0, 0)):
+              out_dims: Optional[Sequence[int]] = None, in_off: Sequence[int] = (0, 0, 0), halo=None,
+              slabs: Optional[Sequence[torch.Tensor]] = None):
     """Stride-1 'same' convolution of the channel concatenation of ``srcs``.
 
     Returns a list of outputs, one per entry of ``dst_channels`` (the output
@@ -116,6 +117,18 @@ def conv_same(srcs: Sequence[torch.Tensor], wpack: torch.Tensor, ksize: int,
     a.bias = _lib.ptr(bias)
     a.status = _lib.status_tensor(srcs[0].device).data_ptr()
     a.force_plain = int(force_plain)
+    if halo is not None:
+        # fused depth halo: landing slabs per (source, face) and the flag words that guard them
+        for si in range(len(srcs)):
+            for f in range(2):
+                a.halo_land[si][f] = halo.land_ptr(si, f)
+        for f in range(2):
+            a.halo_flag[f] = halo.flag_ptr(f)
+        a.halo_epoch = halo.epoch
+        a.halo_wait_s = halo.wait_seconds
+    if slabs is not None:
+        a.slab_out[0], a.slab_out[1] = slabs[0].data_ptr(), slabs[1].data_ptr()
+        a.slab_ld = slabs[0].shape[-1]
     _lib.check(_lib.lib().sb_conv_fwd(C.byref(a), _lib.stream_ptr()), "sb_conv_fwd")
     return outs
 
@@ -167,7 +180,8 @@ def _workspace(device, elems: int) -> torch.Tensor:
 
 
 def conv_wgrad(gy: torch.Tensor, xs: Sequence[torch.Tensor], ksize: int, dw: torch.Tensor,
-               accumulate: bool = False, splits: int = 0, x_off: Sequence[int] = (0, 0, 0)) -> torch.Tensor:
+               accumulate: bool = False, splits: int = 0, x_off: Sequence[int] = (0, 0, 0),
+               x_halo=None) -> torch.Tensor:
     """Weight gradient into ``dw`` (fp32, parameter layout).
 
     ksize 1/3: ``dw`` is [Cout, Cin, k,k,k]; ``gy`` and ``xs`` share the voxel grid.
@@ -190,6 +204,10 @@ def conv_wgrad(gy: torch.Tensor, xs: Sequence[torch.Tensor], ksize: int, dw: tor
         else:
             a.x[i], a.x_c[i], a.x_ld[i] = None, 0, 0
     a.N, a.D, a.H, a.W = n, d, h, w
+    if x_halo is not None:
+        for si, pair in enumerate(x_halo):
+            for f in range(2):
+                a.xhalo[si][f] = pair[f].data_ptr() if pair[f] is not None else None
     a.ksize = ksize
     a.splits = splits
     a.accumulate = 1 if accumulate else 0

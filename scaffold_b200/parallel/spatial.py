@@ -36,7 +36,11 @@ class SpatialContext:
         self.gn_global = gn_stats == "global"
         self.halo_backend = halo_backend
         self.dims: List[int] = layout.sharded_dims()  # tensor dims (NCDHW numbering) that are split
-        self._peer = None
+        self.halo_channel = None
+        if halo_backend == "fused" and self.size > 1 and torch.cuda.is_available() and dist.get_backend() == "nccl":
+            from .halo import HaloChannel
+            if HaloChannel.eligible(layout):
+                self.halo_channel = HaloChannel(layout, self.group)  # collective: every rank of the group
 
     # -- small reductions -------------------------------------------------------
     def all_reduce_sum(self, t: torch.Tensor) -> torch.Tensor:

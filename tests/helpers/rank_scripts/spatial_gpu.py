@@ -1,6 +1,6 @@
 """Rank script (2 GPUs): a U-Net step on a volume split over two spatial shards vs the unsharded step.
 
-usage: spatial_gpu.py <split_dim 2|3|4>
+usage: spatial_gpu.py <split_dim 2|3|4> [nccl|fused]
 Both ranks hold the same weights. Each runs forward + fused loss + backward on its half; gradients are summed
 over the shards. Rank 0 then repeats the step on the whole volume without sharding and compares loss and grads.
 """
@@ -22,10 +22,13 @@ from scaffold_b200.parallel.spatial import SpatialContext  # noqa: E402
 from scaffold_b200.run import attach_spatial  # noqa: E402
 
 split_dim = int(sys.argv[1]) if len(sys.argv) > 1 else 2
+halo_backend = sys.argv[2] if len(sys.argv) > 2 else "nccl"
 shards = [1, 1, 1]
 shards[split_dim - 2] = 2
 layout = ParallelLayout(shards, (2, 3, 4), world, rank)
-spatial = SpatialContext(layout, gn_stats="global")
+spatial = SpatialContext(layout, gn_stats="global", halo_backend=halo_backend)
+if halo_backend == "fused":
+    assert spatial.halo_channel is not None
 
 torch.manual_seed(0)
 n_classes = 5
