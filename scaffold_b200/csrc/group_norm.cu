@@ -48,6 +48,10 @@ struct GnParams {
   float eps;
   int relu;
   float group_elems;  // elements per (n, g) over ALL shards = S_total * C/G
+  const uint32_t* wait_flags;  // optional: peers' "statistics landed" flags (local memory)
+  uint32_t wait_epoch;
+  long long wait_ticks;
+  uint32_t* status;
 };
 
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
@@ -159,6 +163,27 @@ __global__ void __launch_bounds__(GN_THREADS) gn_stats_kernel(const GnParams p) 
   }
 }
 
+// Bounded wait until every peer's statistics landed; returns false (after reporting) on timeout.
+__device__ __forceinline__ bool gn_wait_peers(const GnParams& p, uint32_t site) {
+  if (p.wait_flags == nullptr) return true;
+  int ok = 1;
+  if (threadIdx.x < p.n_parts) {
+    const long long t0 = clock64();
+    while (true) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.wait_flags + threadIdx.x) : "memory");
+      if ((int)(v - p.wait_epoch) >= 0) break;
+      if (clock64() - t0 > p.wait_ticks) {
+        report(p.status, ST_FLAG_TIMEOUT, site, threadIdx.x, p.wait_epoch);
+        ok = 0;
+        break;
+      }
+      __nanosleep(32);
+    }
+  }
+  return __syncthreads_and(ok) != 0;
+}
+
 // merges every partial of sample n, group g, in (part buffer, split) order
 __device__ __forceinline__ void merge_group(const GnParams& p, int n, int g, float& mean, float& rstd) {
   float gn = 0.f, gm = 0.f, g2 = 0.f;
@@ -179,6 +204,7 @@ __device__ __forceinline__ void merge_group(const GnParams& p, int n, int g, flo
 __global__ void __launch_bounds__(GN_THREADS) gn_apply_kernel(const GnParams p) {
   __shared__ float s_mean[256], s_rstd[256];
   const int n = blockIdx.y;
+  if (!gn_wait_peers(p, 61)) return;
   for (int g = threadIdx.x; g < p.G; g += GN_THREADS) {
     float m, r;
     merge_group(p, n, g, m, r);
@@ -296,6 +322,7 @@ __global__ void __launch_bounds__(GN_THREADS) gn_bwd_dx_kernel(const GnParams p)
   float* s_Bt = s_At + p.C;
   const int n = blockIdx.y;
   const int cg = p.C / p.G;
+  if (!gn_wait_peers(p, 62)) return;
   for (int ch = threadIdx.x; ch < p.C; ch += GN_THREADS) {
     float At = 0.f, Bt = 0.f, A0 = 0.f, B0 = 0.f;
     for (int pi = 0; pi < p.n_parts; ++pi) {
@@ -454,6 +481,10 @@ static int gn_fill(const SbGnArgs* a, GnParams& p) {
   p.eps = a->eps;
   p.relu = a->relu;
   p.group_elems = (float)((double)a->S_total * cg);
+  p.wait_flags = a->wait_flags;
+  p.wait_epoch = a->wait_epoch;
+  p.wait_ticks = (long long)((a->wait_s > 0 ? a->wait_s : 2.0) * 1.8e9);
+  p.status = a->status;
   return 0;
 }
 
@@ -515,6 +546,38 @@ extern "C" int sb_gn_bwd_dx(const SbGnArgs* a, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
 
+
+namespace sb {
+struct ShareParams {
+  const float* fin;
+  long long count;
+  float* dst[8];
+  uint32_t* flags[8];
+  int world;
+  uint32_t epoch;
+};
+// one CTA: copy the (tiny) statistics block into every rank's landing slot, then raise the flags
+__global__ void __launch_bounds__(GN_THREADS) gn_share_kernel(const ShareParams p) {
+  for (int r = 0; r < p.world; ++r)
+    for (long long i = threadIdx.x; i < p.count; i += GN_THREADS) p.dst[r][i] = p.fin[i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < p.world)
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[threadIdx.x]), "r"(p.epoch) : "memory");
+}
+}  // namespace sb
+
+extern "C" int sb_gn_share(const float* fin, long long count, void* const* dst, void* const* flags, int world,
+                           unsigned epoch, cudaStream_t stream) {
+  if (world < 1 || world > 8) return SB_ERR_SHAPE;
+  ShareParams p;
+  memset(&p, 0, sizeof(p));
+  p.fin = fin; p.count = count; p.world = world; p.epoch = epoch;
+  for (int r = 0; r < world; ++r) { p.dst[r] = (float*)dst[r]; p.flags[r] = (uint32_t*)flags[r]; }
+  gn_share_kernel<<<1, GN_THREADS, 0, stream>>>(p);
+  sb_count_launch(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
 
 // fin: [N][G][3] (stats) / [N][C][2] (bwd) -- the single-split form the apply / dx kernels merge
 extern "C" int sb_gn_stats_finalize(const float* part, float* fin, int N, int G, int nsplit, cudaStream_t stream) {

@@ -116,7 +116,19 @@ typedef struct {
   int nsplit;
   float eps;
   int relu;
+  // cross-shard statistics over peer memory: when set, the merging kernels first wait (bounded)
+  // until wait_flags[i] >= wait_epoch for every i < n_parts (flags and parts are local memory the
+  // peers pushed into, see sb_gn_share)
+  const unsigned* wait_flags;
+  unsigned wait_epoch;
+  double wait_s;
+  unsigned* status;
 } SbGnArgs;
+
+// Stores `count` floats of `fin` into dst[r] for every r < world (peer pointers valid on this GPU),
+// then publishes `epoch` into flags[r].
+int sb_gn_share(const float* fin, long long count, void* const* dst, void* const* flags, int world,
+                unsigned epoch, cudaStream_t stream);
 
 // number of kernels this library launched so far in the process
 long long sb_launch_count(void);

@@ -31,6 +31,10 @@ class SbGnArgs(C.Structure):
         ("nsplit", C.c_int),
         ("eps", C.c_float),
         ("relu", C.c_int),
+        ("wait_flags", C.c_void_p),
+        ("wait_epoch", C.c_uint),
+        ("wait_s", C.c_double),
+        ("status", C.c_void_p),
     ]
 
 
@@ -38,6 +42,8 @@ for _n in ("sb_gn_stats", "sb_gn_apply", "sb_gn_bwd_partial", "sb_gn_bwd_dx"):
     _lib.register(_n, [C.POINTER(SbGnArgs), C.c_void_p], C.c_int)
 _lib.register("sb_gn_stats_finalize", [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p], C.c_int)
 _lib.register("sb_gn_bwd_finalize", [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p], C.c_int)
+_lib.register("sb_gn_share", [C.c_void_p, C.c_longlong, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int,
+                              C.c_uint, C.c_void_p], C.c_int)
 
 
 def _base(x: torch.Tensor, w, b, groups: int, eps: float, relu: bool, shards: int, nsplit: int = 0) -> SbGnArgs:
@@ -81,9 +87,20 @@ def gn_stats(x, w, b, groups, eps, relu, part: Optional[torch.Tensor] = None,
     return fin
 
 
-def gn_apply(x, w, b, groups, eps, relu, parts: Sequence[int], shards: int = 1):
-    """Pass 2: merge ``parts`` (device pointers, own first) and normalise."""
+def _set_wait(a: SbGnArgs, wait, device) -> None:
+    if wait is not None:
+        a.wait_flags, a.wait_epoch = wait
+        a.wait_s = 2.0
+        a.status = _lib.status_tensor(device).data_ptr()
+
+
+def gn_apply(x, w, b, groups, eps, relu, parts: Sequence[int], shards: int = 1, wait=None):
+    """Pass 2: merge ``parts`` (device pointers, own first) and normalise.
+
+    ``wait`` = (pointer to ``len(parts)`` flag words, epoch): the kernel first waits until every
+    flag reached the epoch (peers push their statistics and then raise the flag)."""
     a = _base(x, w, b, groups, eps, relu, shards, nsplit=1)
+    _set_wait(a, wait, x.device)
     n = x.shape[0]
     y = torch.empty_like(x)
     mean = torch.empty((n, groups), dtype=torch.float32, device=x.device)
@@ -120,8 +137,9 @@ def gn_bwd_partial(dy, x, w, b, mean, rstd, groups, eps, relu, part: Optional[to
     return fin
 
 
-def gn_bwd_dx(dy, x, w, b, mean, rstd, groups, eps, relu, parts: Sequence[int], shards: int = 1):
+def gn_bwd_dx(dy, x, w, b, mean, rstd, groups, eps, relu, parts: Sequence[int], shards: int = 1, wait=None):
     a = _base(x, w, b, groups, eps, relu, shards, nsplit=1)
+    _set_wait(a, wait, x.device)
     a.dy = dy.data_ptr()
     a.mean, a.rstd = mean.data_ptr(), rstd.data_ptr()
     dx = torch.empty_like(x)

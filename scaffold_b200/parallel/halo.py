@@ -141,3 +141,50 @@ class HaloChannel:
     def close(self) -> None:
         self.flags.close()
         self.arena.close()
+
+
+class StatsChannel:
+    """Cross-shard GroupNorm statistics over peer memory.
+
+    ``share(fin)`` launches one tiny kernel that stores this rank's finalised statistics into every
+    rank's landing slot and raises their flags; it returns the LOCAL pointers of all ranks' slots (own
+    first) and the flag block the merging kernel waits on. No collective library call is involved.
+    """
+
+    SLOT_FLOATS = 1 << 14  # 64 KiB per (slot, rank): N * C * 2 floats of the backward statistics fit
+
+    def __init__(self, group):
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.data = PeerBuffer(SLOTS * self.world * self.SLOT_FLOATS * 4, group)
+        self.flags = PeerBuffer(4096, group)
+        self.seq = 0
+
+    def _slot_ptr(self, on_rank: int, slot: int, from_rank: int) -> int:
+        return self.data.ptrs[on_rank] + 4 * self.SLOT_FLOATS * (slot * self.world + from_rank)
+
+    def _flag_ptr(self, on_rank: int, slot: int, position: int) -> int:
+        return self.flags.ptrs[on_rank] + 4 * (slot * self.world + position)
+
+    def _position(self, on_rank: int, from_rank: int) -> int:
+        """Index of ``from_rank`` in ``on_rank``'s merge order: own first, the others in rank order."""
+        if from_rank == on_rank:
+            return 0
+        return from_rank + 1 if from_rank < on_rank else from_rank
+
+    def share(self, fin: torch.Tensor):
+        if fin.numel() > self.SLOT_FLOATS:
+            raise RuntimeError(f"statistics block of {fin.numel()} floats exceeds the slot ({self.SLOT_FLOATS})")
+        slot, epoch = self.seq % SLOTS, self.seq + 1
+        self.seq += 1
+        dst = (_P * self.world)(*[self._slot_ptr(r, slot, self.rank) for r in range(self.world)])
+        flg = (_P * self.world)(*[self._flag_ptr(r, slot, self._position(r, self.rank)) for r in range(self.world)])
+        _lib.check(_lib.lib().sb_gn_share(fin.data_ptr(), fin.numel(), dst, flg, self.world, epoch,
+                                          _lib.stream_ptr()), "sb_gn_share")
+        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        parts = [self._slot_ptr(self.rank, slot, r) for r in order]
+        return parts, (self._flag_ptr(self.rank, slot, 0), epoch)
+
+    def close(self) -> None:
+        self.flags.close()
+        self.data.close()

@@ -37,6 +37,11 @@ class SpatialContext:
         self.halo_backend = halo_backend
         self.dims: List[int] = layout.sharded_dims()  # tensor dims (NCDHW numbering) that are split
         self.halo_channel = None
+        self.stats_channel = None
+        if (halo_backend == "fused" and self.size > 1 and self.size <= 8 and self.gn_global
+                and torch.cuda.is_available() and dist.get_backend() == "nccl"):
+            from .halo import StatsChannel
+            self.stats_channel = StatsChannel(self.group)  # collective
         if halo_backend == "fused" and self.size > 1 and torch.cuda.is_available() and dist.get_backend() == "nccl":
             from .halo import HaloChannel
             if HaloChannel.eligible(layout):
@@ -101,6 +106,9 @@ class SpatialContext:
         if self.size == 1 or not self.gn_global:
             return gk.gn_forward(x, w32, b32, groups, eps, relu)
         fin = gk.gn_stats(x, w32, b32, groups, eps, relu)
+        if self.stats_channel is not None:
+            parts, wait = self.stats_channel.share(fin)
+            return gk.gn_apply(x, w32, b32, groups, eps, relu, parts, shards=self.size, wait=wait)
         parts = self._gather_small(fin)
         return gk.gn_apply(x, w32, b32, groups, eps, relu, [p.data_ptr() for p in parts], shards=self.size)
 
@@ -109,6 +117,9 @@ class SpatialContext:
         if self.size == 1 or not self.gn_global:
             return gk.gn_backward(gy, x, w32, b32, mean, rstd, groups, eps, relu)
         fin = gk.gn_bwd_partial(gy, x, w32, b32, mean, rstd, groups, eps, relu)
+        if self.stats_channel is not None:
+            parts, wait = self.stats_channel.share(fin)
+            return gk.gn_bwd_dx(gy, x, w32, b32, mean, rstd, groups, eps, relu, parts, shards=self.size, wait=wait)
         parts = self._gather_small(fin)
         return gk.gn_bwd_dx(gy, x, w32, b32, mean, rstd, groups, eps, relu, [p.data_ptr() for p in parts],
                             shards=self.size)
