@@ -37,6 +37,8 @@ def parse_args():
     ap.add_argument("--bottleneck-dim", type=int, default=3)
     ap.add_argument("--dc-num-shards", type=int, nargs=3, default=[1, 1, 1])
     ap.add_argument("--grad-allreduce", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--halo-exchange", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--gn-stats", default="global", choices=["global", "per_shard"])
     return ap.parse_args()
 
 
@@ -111,6 +113,8 @@ def main():
     from scaffold_b200.ops import _lib
     from scaffold_b200.ops.optim import FusedClipAdam
     from scaffold_b200.parallel.layout import ParallelLayout
+    from scaffold_b200.parallel.spatial import SpatialContext
+    from scaffold_b200.run import attach_spatial
     from scaffold_b200.train.engine import TrainEngine
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -135,15 +139,22 @@ def main():
         for p in model.parameters():
             dist.broadcast(p.data, 0)
     opt = FusedClipAdam(model.parameters(), lr=1e-3, max_norm=1.0)
-    engine = TrainEngine(model, opt, n_classes, device, layout=layout, grad_backend=args.grad_allreduce)
+    spatial = None
+    if layout.spatial_size > 1:
+        spatial = SpatialContext(layout, gn_stats=args.gn_stats, halo_backend=args.halo_exchange)
+        attach_spatial(model, spatial)
+    engine = TrainEngine(model, opt, n_classes, device, layout=layout, spatial=spatial,
+                         grad_backend=args.grad_allreduce)
 
     S = 2 ** args.scale
-    g = torch.Generator().manual_seed(1234 + rank)
+    local = [S // n for n in layout.num_shards]  # this rank's sub-volume (D, H, W)
+    # ranks of one replica draw the same volume stream; each keeps its own sub-volume
+    g = torch.Generator().manual_seed(1234 + layout.ddp_ind)
     n_host = 2  # rotate pinned host batches so a step never reuses the previous step's staging memory
     host = []
     for _ in range(n_host):
-        img = torch.rand((args.batch, 3, S, S, S), generator=g).pin_memory()
-        msk = torch.randint(0, n_classes, (args.batch, S, S, S), generator=g, dtype=torch.int16).pin_memory()
+        img = torch.rand((args.batch, 3, *local), generator=g).pin_memory()
+        msk = torch.randint(0, n_classes, (args.batch, *local), generator=g, dtype=torch.int16).pin_memory()
         host.append((img, msk))
     dev_batches = [(i.to(device), m.to(device)) for i, m in host]
 
@@ -221,6 +232,8 @@ def main():
             "parallelism": (f"dp{layout.ddp_ranks}" + (f"xsp{sp}{list(layout.num_shards)}" if sp > 1 else "")),
             "batch_per_replica": args.batch,
             "grad_allreduce": args.grad_allreduce if world > 1 else "none",
+            "halo_exchange": args.halo_exchange if sp > 1 else "none",
+            "gn_stats": args.gn_stats,
             "l2_policy": "inputs larger than L2 (activations of one step are several GB; two batches rotate)",
             "final_loss": loss_val,
         },
