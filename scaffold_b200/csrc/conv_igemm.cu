@@ -131,42 +131,52 @@ __global__ void __launch_bounds__(192, 1) igemm_kernel(const __grid_constant__ I
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
+    // Warp-uniform control flow (wait results are voted on) keeps the descriptor arithmetic in
+    // uniform registers; one elected lane issues. Descriptors are (lo, hi) words: a new operand
+    // address is one add.
+    {
+      const bool leader = elect_one();
       const uint32_t idesc = make_idesc_bf16(128, p.BN, 0, 0);
       const uint32_t swz = swizzle_code_for(rowb);
       const int rh = p.TH + p.KHS - 1;             // rows per w column of the A box
       // 8-row groups are contiguous unless the box carries an h halo (then one w step apart)
-      const uint32_t sbo = (uint32_t)(p.KHS > 1 ? rh : 8) * rowb;
-      const uint32_t b_shift = (uint32_t)p.BN * rowb;
-      uint32_t it = 0, tcount = 0;
+      const uint32_t a_hi = desc_hi((uint32_t)(p.KHS > 1 ? rh : 8) * rowb, swz);
+      const uint32_t b_hi = desc_hi(8u * rowb, swz);
+      const uint32_t b_shift = ((uint32_t)p.BN * rowb) >> 4;
+      const uint32_t a_wstep = ((uint32_t)(p.KHS > 1 ? rh : p.TH) * rowb) >> 4;
+      const uint32_t a_hstep = (uint32_t)rowb >> 4;
+      const int ksteps = p.BK / 16;
+      const uint32_t s0 = smem_u32(smem);
+      uint32_t stage = 0, sph = 0, tcount = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++tcount) {
         const uint32_t buf = tcount & 1u;
         const uint32_t bph = (tcount >> 1) & 1u;
-        if (!mbar_wait(&tempty_bar[buf], bph ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&tempty_bar[buf], bph ^ 1u, abort_flag, p.status, 2))) { ok = false; break; }
         tc_fence_after();
         const uint32_t acc = tmem_base + buf * 128u;
-        for (int ki = 0; ki < kiters; ++ki, ++it) {
-          const int s = it % p.stages;
-          const uint32_t ph = (it / p.stages) & 1u;
-          if (!mbar_wait(&full_bar[s], ph, abort_flag, p.status, 3)) { ok = false; break; }
+        for (int ki = 0; ki < kiters; ++ki) {
+          if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], sph, abort_flag, p.status, 3))) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + (size_t)s * p.stage_bytes);
-          const uint32_t sbm = sa + p.a_bytes;
+          const uint32_t sa = s0 + stage * (uint32_t)p.stage_bytes;
+          const uint32_t a_lo0 = desc_lo(sa, 16u);
+          const uint32_t b_lo0 = desc_lo(sa + p.a_bytes, 16u);
           for (int kh = 0; kh < p.KHS; ++kh) {
             for (int kw = 0; kw < p.KWS; ++kw) {
-              const uint32_t a0 = sa + (uint32_t)(kw * (p.KHS > 1 ? rh : p.TH) + kh) * rowb;
-              const uint32_t b0 = sbm + (uint32_t)(kh * p.KWS + kw) * b_shift;
-              for (int k = 0; k < p.BK / 16; ++k) {
-                const uint64_t da = make_smem_desc(a0 + k * 32u, 16u, sbo, swz);
-                const uint64_t db = make_smem_desc(b0 + k * 32u, 16u, 8u * rowb, swz);
-                tc_mma_bf16(acc, da, db, idesc, (ki | kh | kw | k) != 0 ? 1u : 0u);
+              const uint32_t a_lo = a_lo0 + kw * a_wstep + kh * a_hstep;
+              const uint32_t b_lo = b_lo0 + (uint32_t)(kh * p.KWS + kw) * b_shift;
+              if (leader) {
+                for (int k = 0; k < ksteps; ++k)
+                  tc_mma_bf16_pred(acc, a_lo + 2u * k, a_hi, b_lo + 2u * k, b_hi, idesc,
+                                   (ki | kh | kw | k) != 0 ? 1u : 0u);
               }
             }
           }
-          tc_commit(&empty_bar[s]);
+          if (leader) tc_commit(&empty_bar[stage]);
+          __syncwarp();
+          if (++stage == (uint32_t)p.stages) { stage = 0; sph ^= 1u; }
         }
-        if (ok) tc_commit(&tfull_bar[buf]);
+        if (ok && leader) tc_commit(&tfull_bar[buf]);
       }
     }
   } else {

@@ -121,31 +121,37 @@ __global__ void __launch_bounds__(192, 1) wgrad_kernel(const __grid_constant__ W
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // warp-uniform loop, one elected lane issues (descriptor arithmetic stays in uniform registers)
+    {
+      const bool leader = elect_one();
       const uint32_t idesc = make_idesc_bf16(p.umma_m, p.NT, 1, 1);
       const uint32_t rowm = p.CBm * 2, rown = p.CBn * 2;
-      const uint32_t swzm = swizzle_code_for(rowm), swzn = swizzle_code_for(rown);
       // MN-major: LBO = distance between channel blocks, SBO = distance between 8-voxel groups
       const uint32_t lbom = p.m_boxes > 1 ? (uint32_t)p.boxm_bytes : 0u;
       const uint32_t lbon = p.n_boxes > 1 ? (uint32_t)p.boxn_bytes : 0u;
+      const uint32_t m_hi = desc_hi(8u * rowm, swizzle_code_for(rowm));
+      const uint32_t n_hi = desc_hi(8u * rown, swizzle_code_for(rown));
+      const uint32_t m_step = (16u * rowm) >> 4, n_step = (16u * rown) >> 4, n_shift = (8u * rown) >> 4;
+      const int ksteps = p.KV / 16;
+      const uint32_t s0 = smem_u32(smem);
+      uint32_t stage = 0, sph = 0;
       bool ok = true;
       for (int i = 0; i < nblk && ok; ++i) {
-        const int s = i % p.stages;
-        const uint32_t ph = (i / p.stages) & 1u;
-        if (!mbar_wait(&full_bar[s], ph, abort_flag, p.status, 12)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], sph, abort_flag, p.status, 12))) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sm = smem_u32(smem + (size_t)s * p.stage_bytes);
-        const uint32_t sn = sm + p.m_bytes;
-        for (int kw = 0; kw < p.KWS; ++kw) {
-          for (int k = 0; k < p.KV / 16; ++k) {
-            const uint64_t da = make_smem_desc(sm + k * 16u * rowm, lbom, 8u * rowm, swzm);
-            const uint64_t db = make_smem_desc(sn + kw * 8u * rown + k * 16u * rown, lbon, 8u * rown, swzn);
-            tc_mma_bf16(tmem_base + kw * p.NT, da, db, idesc, (i | k) != 0 ? 1u : 0u);
-          }
+        const uint32_t sm = s0 + stage * (uint32_t)p.stage_bytes;
+        const uint32_t m_lo = desc_lo(sm, lbom), n_lo = desc_lo(sm + p.m_bytes, lbon);
+        if (leader) {
+          for (int kw = 0; kw < p.KWS; ++kw)
+            for (int k = 0; k < ksteps; ++k)
+              tc_mma_bf16_pred(tmem_base + kw * p.NT, m_lo + k * m_step, m_hi, n_lo + kw * n_shift + k * n_step, n_hi,
+                               idesc, (i | k) != 0 ? 1u : 0u);
+          tc_commit(&empty_bar[stage]);
         }
-        tc_commit(&empty_bar[s]);
+        __syncwarp();
+        if (++stage == (uint32_t)p.stages) { stage = 0; sph ^= 1u; }
       }
-      if (ok) tc_commit(&done_bar);
+      if (ok && leader) tc_commit(&done_bar);
     }
   } else {
     const int q = warp & 3;
