@@ -52,7 +52,7 @@ def rot(n, make):
     return [make() for _ in range(n)]
 
 
-def run(op, cin, cout, size, batch, iters, ref=True):
+def run(op, cin, cout, size, batch, iters, ref=True, kd_fused=True):
     tf_peak, bw_peak, which = peaks()
     n, s = batch, size
     dev = "cuda"
@@ -66,9 +66,9 @@ def run(op, cin, cout, size, batch, iters, ref=True):
         dw = torch.empty_like(w)
         flops = 2.0 * n * s ** 3 * max(cin, 16) * cout * 27
         if op == "conv_fwd":
-            fn = lambda i: ck.conv_same([xs[i % nbuf]], wf, 3, [cout])
+            fn = lambda i: ck.conv_same([xs[i % nbuf]], wf, 3, [cout], kd_fused=kd_fused)
         elif op == "conv_dgrad":
-            fn = lambda i: ck.conv_same([gys[i % nbuf]], wd, 3, [max(cin, 16)])
+            fn = lambda i: ck.conv_same([gys[i % nbuf]], wd, 3, [max(cin, 16)], kd_fused=kd_fused)
         else:
             fn = lambda i: ck.conv_wgrad(gys[i % nbuf], [xs[i % nbuf]], 3, dw)
         ms = timeit(fn, iters)
@@ -185,6 +185,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-ref", action="store_true")
+    ap.add_argument("--no-kd-fused", action="store_true", help="narrow-output 3x3x3 convs on the one-tap-per-MMA kernel")
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--json", action="store_true")
     a = ap.parse_args()
@@ -204,7 +205,7 @@ def main():
             rows.append(run(extra[0], extra[1], extra[2], extra[3], a.batch, a.iters, not a.no_ref))
             print(fmt(rows[-1]), flush=True)
     else:
-        rows.append(run(a.op, a.cin, a.cout, a.size, a.batch, a.iters, not a.no_ref))
+        rows.append(run(a.op, a.cin, a.cout, a.size, a.batch, a.iters, not a.no_ref, not a.no_kd_fused))
         print(fmt(rows[-1]), flush=True)
     if a.json:
         print(json.dumps(rows))

@@ -408,13 +408,18 @@ using namespace sb;
 
 // Stride-1 "same" convolution, k in {1,3}; also backward-data when the caller
 // packs the weights transposed and tap-flipped.
-namespace sb { int conv_plane_launch(const SbConvArgs* a, cudaStream_t stream); }
+namespace sb {
+int conv_plane_launch(const SbConvArgs* a, cudaStream_t stream);
+int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream);
+}
 
 // force_plain: 0 = automatic (plane-walk kernel when the shape is eligible, else this file's
 // generic kernel), 1 = generic kernel one tap per load, 2 = generic kernel with the w-shift
 // reuse, 3 = generic kernel with the (h, w)-shift reuse.
 extern "C" int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream) {
   if (a->force_plain == 0) {
+    const int p3 = conv_plane3_launch(a, stream);
+    if (p3 >= 0) return p3;
     const int prc = conv_plane_launch(a, stream);
     if (prc >= 0) return prc;
   }

@@ -52,6 +52,9 @@ typedef struct {
   // (gradient of the halo) go to slab_out[0] / slab_out[1] ([N,1,H,W,slab_ld]), the rest to dst.
   void* slab_out[2];
   int slab_ld;
+  // Optional second packing of the same 3x3x3 weights, taps ordered (kh, kw, 2-kd): lets the
+  // kd-fused kernel (conv_plane3.cu) fetch the three kd taps of a (kh, kw) pair as one box.
+  const void* wpack_kd;
 } SbConvArgs;
 
 // k=2,s=2 transposed convolution. Forward: src [N,D,H,W,cin] -> dst

@@ -121,7 +121,8 @@ def accept(stats: np.ndarray, normalize: float, variance_threshold: float) -> Tu
     reason 0 ok, 1 non-finite, 2 low variance, 3 runaway.
     """
     stats = np.atleast_2d(stats)
-    rng = stats[:, 3:6] - stats[:, 0:3]
+    with np.errstate(invalid="ignore", over="ignore"):
+        rng = stats[:, 3:6] - stats[:, 0:3]
     finite = (stats[:, 14] == 0) & np.isfinite(rng).all(1) & (rng > 0).all(1)
     with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
         var_n = stats[:, 9:12] * ((2.0 * normalize) / rng) ** 2

@@ -52,6 +52,7 @@ class SbConvArgs(C.Structure):
         ("halo_wait_s", C.c_double),
         ("slab_out", C.c_void_p * 2),
         ("slab_ld", C.c_int),
+        ("wpack_kd", C.c_void_p),
     ]
 
 

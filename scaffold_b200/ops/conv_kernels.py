@@ -27,13 +27,26 @@ def pad_channels(c: int) -> int:
 # ---------------------------------------------------------------------------
 # weight packing (bf16 operand copies; the fp32 parameter stays the master)
 # ---------------------------------------------------------------------------
+def kd_order(pack: torch.Tensor) -> torch.Tensor:
+    """Reorder a 27-tap pack from (kd, kh, kw) to (kh, kw, 2-kd): the operand of the kd-fused plane kernel."""
+    rows, k = pack.shape[1:]
+    return pack.view(3, 3, 3, rows, k).flip(0).permute(1, 2, 0, 3, 4).reshape(27, rows, k).contiguous()
+
+
+def _attach_kd_order(pack: torch.Tensor) -> torch.Tensor:
+    # narrow outputs (<= 64 rows per tap) run the kd-fused kernel, which wants the second ordering
+    if pack.shape[0] == 27 and pack.shape[1] <= 64 and pack.shape[2] % 32 == 0:
+        pack.kd_order = kd_order(pack)
+    return pack
+
+
 def pack_weight_fwd(w: torch.Tensor) -> torch.Tensor:
     """[Cout, Cin, k, k, k] -> bf16 [taps, cout_pad, cin_pad] (taps = kd,kh,kw row-major)."""
     co, ci = w.shape[:2]
     taps = w.shape[2] * w.shape[3] * w.shape[4]
     out = torch.zeros(taps, pad_channels(co), pad_channels(ci), dtype=torch.bfloat16, device=w.device)
     out[:, :co, :ci] = w.reshape(co, ci, taps).permute(2, 0, 1)
-    return out
+    return _attach_kd_order(out)
 
 
 def pack_weight_dgrad(w: torch.Tensor) -> torch.Tensor:
@@ -42,7 +55,7 @@ def pack_weight_dgrad(w: torch.Tensor) -> torch.Tensor:
     taps = w.shape[2] * w.shape[3] * w.shape[4]
     out = torch.zeros(taps, pad_channels(ci), pad_channels(co), dtype=torch.bfloat16, device=w.device)
     out[:, :ci, :co] = w.reshape(co, ci, taps).flip(2).permute(2, 1, 0)
-    return out
+    return _attach_kd_order(out)
 
 
 def pack_weight_convT_fwd(w: torch.Tensor) -> torch.Tensor:
@@ -73,13 +86,14 @@ def conv_same(srcs: Sequence[torch.Tensor], wpack: torch.Tensor, ksize: int,
               dst_channels: Sequence[int], bias: Optional[torch.Tensor] = None,
               force_plain: bool = False, out: Optional[Sequence[torch.Tensor]] = None,
               out_dims: Optional[Sequence[int]] = None, in_off: Sequence[int] = (0, 0, 0), halo=None,
-              slabs: Optional[Sequence[torch.Tensor]] = None):
+              slabs: Optional[Sequence[torch.Tensor]] = None, kd_fused: bool = True):
     """Stride-1 'same' convolution of the channel concatenation of ``srcs``.
 
     Returns a list of outputs, one per entry of ``dst_channels`` (the output
     channels are split in that order). ``out_dims`` (D, H, W) and ``in_off`` describe
     halo'd sources of a sharded volume: output voxel 0 sits at ``in_off`` inside the
     sources (negative offsets read zeros, which is how backward-data grows a halo).
+    ``kd_fused=False`` keeps a narrow-output call on the one-tap-per-MMA plane kernel.
     """
     for s in srcs:
         _chk_act(s)
@@ -101,6 +115,8 @@ def conv_same(srcs: Sequence[torch.Tensor], wpack: torch.Tensor, ksize: int,
     a.ksize = ksize
     a.wpack = wpack.data_ptr()
     a.cout_pad = wpack.shape[1]
+    kd = getattr(wpack, "kd_order", None) if kd_fused else None
+    a.wpack_kd = kd.data_ptr() if kd is not None else None
     if wpack.shape[2] != sum(s.shape[4] for s in srcs):
         raise ValueError(f"packed weight K {wpack.shape[2]} != source channels {[s.shape[4] for s in srcs]}")
     outs = list(out) if out is not None else [

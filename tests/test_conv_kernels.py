@@ -40,7 +40,15 @@ def pad_c(x, c):  # pad channel dim (dim 1) of NCDHW with zeros
 
 
 FWD_CASES = [
-    # N, D, H, W, Cin(list), Cout, k, kernel mode (0 auto / plane-walk, 1 plain, 2 w-shift, 3 hw-shift)
+    # N, D, H, W, Cin(list), Cout, k, kernel mode (0 auto: kd-fused plane kernel for <= 64 output channels else
+    # plane-walk, 1 plain, 2 w-shift, 3 hw-shift, 4 plane-walk without kd fusion)
+    (1, 4, 16, 32, [64], 64, 3, 4),
+    (2, 7, 24, 48, [64], 64, 3, 4),
+    (1, 2, 16, 16, [64, 64], 64, 3, 4),
+    (1, 3, 12, 20, [32], 32, 3, 4),
+    (1, 9, 16, 16, [32, 96], 48, 3, 0),
+    (1, 1, 8, 16, [64], 64, 3, 0),
+    (3, 6, 40, 40, [64], 16, 3, 0),
     (1, 4, 16, 32, [64], 64, 3, 0),
     (1, 4, 16, 32, [64], 64, 3, 1),
     (1, 4, 16, 32, [64], 64, 3, 2),
@@ -86,7 +94,8 @@ def test_conv_fwd_bitwise(case):
     if bias is not None:
         bpad = torch.zeros(cpad, device="cuda")
         bpad[:cout] = bias
-    (y,) = ck.conv_same(srcs, wpack, k, [cpad], bias=bpad, force_plain=plain)
+    (y,) = ck.conv_same(srcs, wpack, k, [cpad], bias=bpad, force_plain=0 if plain == 4 else plain,
+                        kd_fused=plain != 4)
     torch.cuda.synchronize()
     _lib.check_status()
     got = ncdhw(y)[:, :cout]
