@@ -91,6 +91,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
+#ifdef SB_WAIT_BACKOFF_NS
+    __nanosleep(SB_WAIT_BACKOFF_NS);
+#endif
     if ((++spins & 63u) == 0u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > SB_WAIT_LIMIT_TICKS) {
@@ -259,6 +262,12 @@ __host__ __device__ __forceinline__ uint32_t swizzle_code_for(int row_bytes) {
   return row_bytes == 128 ? 2u : row_bytes == 64 ? 4u : row_bytes == 32 ? 6u : 0u;
 }
 
+// One 32-byte global store (needs a 32-byte aligned address).
+__device__ __forceinline__ void st_global_v8(void* ptr, uint4 lo, uint4 hi) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(lo.x), "r"(lo.y), "r"(lo.z),
+               "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+               : "memory");
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&t);

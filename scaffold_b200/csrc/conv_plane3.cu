@@ -1,4 +1,4 @@
-// Plane-walk 3x3x3 convolution, kd-fused variant for narrow outputs (BN <= 64 channels per tile).
+// Plane-walk 3x3x3 convolution, kd-fused variant: output channels in tiles of BN <= 64.
 //
 // With 64 output channels a 128 x 64 x 16 MMA re-reads its 4 KB activation tile from shared memory
 // for only 32 tensor-core cycles of work: operand delivery, not math, is the limit. The same
@@ -31,6 +31,7 @@ struct Plane3Params {
   CUtensorMap mapA[2];
   CUtensorMap mapB;
   int BN, TD;
+  int nsets, nbufs, tmem_cols;  // plane sets / accumulator buffers per CTA (1 when two CTAs share an SM)
   int b_slots, a_slot_bytes, b_slot_bytes, a_tx, b_tx;
   int N, D, H, W;
   int tiles_h, tiles_w, groups_d, tiles_co, num_jobs;
@@ -39,6 +40,7 @@ struct Plane3Params {
   __nv_bfloat16* out0;
   __nv_bfloat16* out1;
   int width0, width1, ld0, ld1;
+  int wide;  // widths and strides are multiples of 16 channels: 32-byte stores
   const float* bias;
   uint32_t* status;
   unsigned long long* stall;  // optional stall counters (clock ticks summed over CTAs), null = off
@@ -57,16 +59,16 @@ __device__ __forceinline__ P3Job p3_decode(const Plane3Params& p, int job) {
 }
 
 template <int TD>
-__global__ void __launch_bounds__(224, 1) conv_plane3_kernel(const __grid_constant__ Plane3Params p) {
+__global__ void __launch_bounds__(224, 2) conv_plane3_kernel(const __grid_constant__ Plane3Params p) {
   constexpr int planes = TD + 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* smem_b = smem + (size_t)2 * planes * p.a_slot_bytes;
-  __shared__ uint64_t a_full[2 * planes];
+  uint8_t* smem_b = smem + (size_t)p.nsets * planes * p.a_slot_bytes;
+  __shared__ uint64_t a_full[2];
   __shared__ uint64_t set_empty[2];
   __shared__ uint64_t b_full[P3_MAX_B], b_empty[P3_MAX_B];
   __shared__ uint64_t tfull[2];
-  __shared__ uint64_t tempty[8];
+  __shared__ uint64_t tempty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_s;
   volatile uint32_t* abort_flag = &abort_s;
@@ -74,13 +76,11 @@ __global__ void __launch_bounds__(224, 1) conv_plane3_kernel(const __grid_consta
 
   if (threadIdx.x == 0) {
     abort_s = 0;
-    for (int s = 0; s < 2 * planes; ++s) mbar_init(&a_full[s], 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&set_empty[s], 1); mbar_init(&tfull[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&a_full[s], 1); mbar_init(&set_empty[s], 1); mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 4); }
     for (int s = 0; s < p.b_slots; ++s) { mbar_init(&b_full[s], 1); mbar_init(&b_empty[s], 1); }
-    for (int a = 0; a < 8; ++a) mbar_init(&tempty[a], 4);
     mbar_fence_init();
   }
-  if (warp == 0) { tmem_alloc(&tmem_base_s, 512); tmem_relinquish(); }
+  if (warp == 0) { tmem_alloc(&tmem_base_s, (uint32_t)p.tmem_cols); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -96,14 +96,15 @@ __global__ void __launch_bounds__(224, 1) conv_plane3_kernel(const __grid_consta
       for (int job = blockIdx.x; job < p.num_jobs && ok; job += gridDim.x) {
         const P3Job jc = p3_decode(p, job);
         for (int cb = 0; cb < p.cblks && ok; ++cb, ++uses) {
-          const uint32_t set = uses & 1u, ph = (uses >> 1) & 1u;
+          const uint32_t set = p.nsets == 2 ? (uses & 1u) : 0u;
+          const uint32_t ph = (p.nsets == 2 ? (uses >> 1) : uses) & 1u;
           if (!mbar_wait(&set_empty[set], ph ^ 1u, abort_flag, p.status, 71)) { ok = false; break; }
           const int second = cb >= p.cblks0 ? 1 : 0;
           const int c = (second ? cb - p.cblks0 : cb) * P3_BK;
+          mbar_expect_tx(&a_full[set], (uint32_t)(planes * p.a_tx));
           for (int j = 0; j < planes; ++j) {
             const int s = set * planes + j;
-            mbar_expect_tx(&a_full[s], (uint32_t)p.a_tx);
-            tma_load_5d(smem + (size_t)s * p.a_slot_bytes, &p.mapA[second], &a_full[s], c, jc.h0 - 1 + p.off_h,
+            tma_load_5d(smem + (size_t)s * p.a_slot_bytes, &p.mapA[second], &a_full[set], c, jc.h0 - 1 + p.off_h,
                         jc.w0 - 1 + p.off_w, jc.d0 - 1 + j + p.off_d, jc.n);
           }
         }
@@ -130,10 +131,11 @@ __global__ void __launch_bounds__(224, 1) conv_plane3_kernel(const __grid_consta
     }
   } else if (warp == 2) {
     // ------------------------------- MMA issuer -------------------------------
-    // Measured on this part: one thread can keep the tensor pipe full only if nothing but integer
-    // adds sits between consecutive tcgen05.mma (the pipe accepts about one instruction ahead), and
-    // a 128 x N x 16 MMA costs max(N/2, 32 + N/4) cycles. So all waits are hoisted out of the MMA
-    // runs: accumulators at job start, planes at channel-block start, weights once per (kh, kw).
+    // Measured on this part: one thread keeps the tensor pipe full only if nothing but integer adds
+    // sits between consecutive tcgen05.mma (the pipe accepts about one instruction ahead), and a
+    // 128 x N x 16 MMA costs max(N/2, 32 + N/4) cycles. So no wait sits in front of an MMA run: the
+    // operands of step g+1 (weights; at a channel-block change the plane set; at a job change the
+    // accumulators) are awaited in the middle of step g, behind the N = 192 MMAs already queued.
     const bool leader = elect_one();
     const uint32_t swz = swizzle_code_for(P3_ROWB);
     const uint32_t a_hi = desc_hi((uint32_t)P3_RH * P3_ROWB, swz);
@@ -143,70 +145,101 @@ __global__ void __launch_bounds__(224, 1) conv_plane3_kernel(const __grid_consta
     for (int n = 1; n <= 3; ++n) idesc[n] = make_idesc_bf16(128, n * p.BN, 0, 0);
     const uint32_t sa0 = smem_u32(smem), sb0 = smem_u32(smem_b);
     const uint32_t b_tap = ((uint32_t)p.BN * P3_ROWB) >> 4;  // one tap's rows, in descriptor units
+    const uint32_t a_step = (uint32_t)p.a_slot_bytes >> 4;
     uint32_t uses = 0, b_slot = 0, b_par = 0, jcount = 0;
     bool ok = true;
     long long st_b = 0, st_a = 0, st_t = 0;
     const long long st_begin = clock64();
 #define P3_TIMED(counter, expr) \
   [&]() { const long long c0_ = p.stall ? clock64() : 0; const bool r_ = (expr); if (p.stall) counter += clock64() - c0_; return r_; }()
+#define P3_WAIT(counter, bar, par, site) P3_TIMED(counter, __all_sync(0xffffffffu, mbar_wait(bar, par, abort_flag, p.status, site)))
+    // With one plane set / one accumulator buffer (two CTAs per SM hide each other's gaps) the
+    // next set or buffer is the current one: it can only be awaited after this step's commit.
+    const bool sets2 = p.nsets == 2, bufs2 = p.nbufs == 2;
+    if (blockIdx.x < p.num_jobs) ok = P3_WAIT(st_b, &b_full[0], 0u, 73);
     for (int job = blockIdx.x; job < p.num_jobs && ok; job += gridDim.x, ++jcount) {
-      const uint32_t buf = jcount & 1u, buf_par = ((jcount >> 1) & 1u) ^ 1u;
-      for (int t = 0; t < TD; ++t)
-        if (!P3_TIMED(st_t, __all_sync(0xffffffffu, mbar_wait(&tempty[buf * TD + t], buf_par, abort_flag, p.status, 75)))) { ok = false; break; }
-      if (!ok) break;
+      const uint32_t buf = bufs2 ? (jcount & 1u) : 0u;
+      const bool last_job = job + (int)gridDim.x >= p.num_jobs;
       const uint32_t acc0 = tmem_base + buf * TD * p.BN;
+      if (!bufs2 || jcount == 0) {
+        if (!P3_WAIT(st_t, &tempty[buf], ((bufs2 ? (jcount >> 1) : jcount) & 1u) ^ 1u, 75)) { ok = false; break; }
+      }
       for (int cb = 0; cb < p.cblks && ok; ++cb, ++uses) {
-        const uint32_t set = uses & 1u, sph = (uses >> 1) & 1u;
-        for (int j = 0; j < planes; ++j)
-          if (!P3_TIMED(st_a, __all_sync(0xffffffffu, mbar_wait(&a_full[set * planes + j], sph, abort_flag, p.status, 74)))) { ok = false; break; }
-        if (!ok) break;
+        const uint32_t set = sets2 ? (uses & 1u) : 0u;
+        const bool last_cb = cb + 1 == p.cblks;
+        if (!sets2 || uses == 0) {
+          if (!P3_WAIT(st_a, &a_full[set], (sets2 ? (uses >> 1) : uses) & 1u, 74)) { ok = false; break; }
+        }
         const uint32_t a_set = desc_lo(sa0 + set * planes * (uint32_t)p.a_slot_bytes, 16u);
-        const uint32_t a_step = (uint32_t)p.a_slot_bytes >> 4;
         for (int khw = 0; khw < 9; ++khw) {
           const int kh = khw / 3, kw = khw - kh * 3;
-          if (!P3_TIMED(st_b, __all_sync(0xffffffffu, mbar_wait(&b_full[b_slot], b_par, abort_flag, p.status, 73)))) { ok = false; break; }
           tc_fence_after();
           const uint32_t b_lo0 = desc_lo(sb0 + b_slot * (uint32_t)p.b_slot_bytes, 16u);
           const uint32_t a_tap = a_set + (((uint32_t)(kw * P3_RH + kh) * P3_ROWB) >> 4);
-          if ((cb | khw) == 0) {
-            // first touch of each accumulator overwrites: one N = BN MMA per (input plane, output plane)
+          const bool first = (cb | khw) == 0;
+          uint32_t nb_slot = b_slot + 1, nb_par = b_par;
+          if (nb_slot == (uint32_t)p.b_slots) { nb_slot = 0; nb_par ^= 1u; }
 #pragma unroll
-            for (int j = 0; j < planes; ++j) {
+          for (int half = 0; half < 2; ++half) {
+            if (first) {
+              // first touch of each accumulator overwrites: one N = BN MMA per (input plane, output plane)
 #pragma unroll
-              for (int t = (j - 2 > 0 ? j - 2 : 0); t <= (j < TD - 1 ? j : TD - 1); ++t) {
+              for (int j = half * (planes / 2); j < (half ? planes : planes / 2); ++j) {
+#pragma unroll
+                for (int t = (j - 2 > 0 ? j - 2 : 0); t <= (j < TD - 1 ? j : TD - 1); ++t) {
+                  if (leader) {
+#pragma unroll
+                    for (int k = 0; k < 2; ++k)
+                      tc_mma_bf16_pred(acc0 + t * p.BN, a_tap + j * a_step + 2u * k, a_hi,
+                                       b_lo0 + (uint32_t)(2 - (j - t)) * b_tap + 2u * k, b_hi, idesc[1],
+                                       (t == j && k == 0) ? 0u : 1u);
+                  }
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = half * (planes / 2); j < (half ? planes : planes / 2); ++j) {
+                const int t_lo = j - 2 > 0 ? j - 2 : 0;
+                const int t_hi = j < TD - 1 ? j : TD - 1;
                 if (leader) {
 #pragma unroll
                   for (int k = 0; k < 2; ++k)
-                    tc_mma_bf16_pred(acc0 + t * p.BN, a_tap + j * a_step + 2u * k, a_hi,
-                                     b_lo0 + (uint32_t)(2 - (j - t)) * b_tap + 2u * k, b_hi, idesc[1],
-                                     (t == j && k == 0) ? 0u : 1u);
+                    tc_mma_bf16_acc(acc0 + t_lo * p.BN, a_tap + j * a_step + 2u * k, a_hi,
+                                    b_lo0 + (uint32_t)(2 - (j - t_lo)) * b_tap + 2u * k, b_hi, idesc[t_hi - t_lo + 1]);
                 }
               }
             }
-          } else {
-#pragma unroll
-            for (int j = 0; j < planes; ++j) {
-              const int t_lo = j - 2 > 0 ? j - 2 : 0;
-              const int t_hi = j < TD - 1 ? j : TD - 1;
-              if (leader) {
-#pragma unroll
-                for (int k = 0; k < 2; ++k)
-                  tc_mma_bf16_acc(acc0 + t_lo * p.BN, a_tap + j * a_step + 2u * k, a_hi,
-                                  b_lo0 + (uint32_t)(2 - (j - t_lo)) * b_tap + 2u * k, b_hi, idesc[t_hi - t_lo + 1]);
+            if (half == 0) {
+              // look ahead: what the next step reads
+              const bool more = !(last_job && last_cb && khw == 8);
+              if (more) {
+                if (!P3_WAIT(st_b, &b_full[nb_slot], nb_par, 73)) { ok = false; break; }
+                if (khw == 8) {
+                  const uint32_t nu = uses + 1;
+                  if (sets2 && !P3_WAIT(st_a, &a_full[nu & 1u], (nu >> 1) & 1u, 74)) { ok = false; break; }
+                  if (last_cb && bufs2) {
+                    const uint32_t nj = jcount + 1;
+                    if (!P3_WAIT(st_t, &tempty[nj & 1u], ((nj >> 1) & 1u) ^ 1u, 75)) { ok = false; break; }
+                  }
+                }
               }
             }
           }
-          if (leader) tc_commit(&b_empty[b_slot]);
+          if (!ok) break;
+          if (leader) {
+            tc_commit(&b_empty[b_slot]);
+            if (khw == 8) {
+              tc_commit(&set_empty[set]);
+              if (last_cb) tc_commit(&tfull[buf]);
+            }
+          }
           __syncwarp();
-          if (++b_slot == (uint32_t)p.b_slots) { b_slot = 0; b_par ^= 1u; }
+          b_slot = nb_slot;
+          b_par = nb_par;
         }
-        if (!ok) break;
-        if (leader) tc_commit(&set_empty[set]);
-        __syncwarp();
       }
-      if (ok && leader) tc_commit(&tfull[buf]);
-      __syncwarp();
     }
+#undef P3_WAIT
 #undef P3_TIMED
     if (p.stall && lane == 0) {
       atomicAdd(&p.stall[0], (unsigned long long)(clock64() - st_begin));
@@ -224,7 +257,7 @@ __global__ void __launch_bounds__(224, 1) conv_plane3_kernel(const __grid_consta
     long long st_f = 0;
     const long long ep_begin = clock64();
     for (int job = blockIdx.x; job < p.num_jobs && ok; job += gridDim.x, ++jcount) {
-      const uint32_t buf = jcount & 1u, use = jcount >> 1;
+      const uint32_t buf = p.nbufs == 2 ? (jcount & 1u) : 0u, use = p.nbufs == 2 ? (jcount >> 1) : jcount;
       const long long c0 = p.stall ? clock64() : 0;
       if (!mbar_wait(&tfull[buf], use & 1u, abort_flag, p.status, 76)) { ok = false; break; }
       if (p.stall) st_f += clock64() - c0;
@@ -242,35 +275,38 @@ __global__ void __launch_bounds__(224, 1) conv_plane3_kernel(const __grid_consta
           tmem_ld_32x16(tbase + c0, v);
           tmem_ld_wait();
           if (valid) {
+            const int col0 = jc.co0 + c0;
+            uint4 o[2];
 #pragma unroll
             for (int g = 0; g < 2; ++g) {
-              const int col = jc.co0 + c0 + g * 8;
               float f[8];
 #pragma unroll
               for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[g * 8 + e]);
-              __nv_bfloat16* dst = nullptr;
-              if (col < p.width0) {
-                dst = p.out0 + vox * p.ld0 + col;
-                if (p.bias) {
+              if (p.bias && col0 + g * 8 < p.width0) {
 #pragma unroll
-                  for (int e = 0; e < 8; ++e) f[e] += p.bias[col + e];
-                }
-              } else if (col - p.width0 < p.width1) {
-                dst = p.out1 + vox * p.ld1 + (col - p.width0);
+                for (int e = 0; e < 8; ++e) f[e] += p.bias[col0 + g * 8 + e];
               }
-              if (dst) {
-                uint4 o;
-                o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
-                o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
-                *reinterpret_cast<uint4*>(dst) = o;
+              o[g].x = pack_bf16x2(f[0], f[1]); o[g].y = pack_bf16x2(f[2], f[3]);
+              o[g].z = pack_bf16x2(f[4], f[5]); o[g].w = pack_bf16x2(f[6], f[7]);
+            }
+            if (p.wide) {
+              // destinations split at a multiple of 16 channels: one 32-byte store per 16 channels
+              if (col0 < p.width0) st_global_v8(p.out0 + vox * p.ld0 + col0, o[0], o[1]);
+              else if (col0 - p.width0 < p.width1) st_global_v8(p.out1 + vox * p.ld1 + (col0 - p.width0), o[0], o[1]);
+            } else {
+#pragma unroll
+              for (int g = 0; g < 2; ++g) {
+                const int col = col0 + g * 8;
+                if (col < p.width0) *reinterpret_cast<uint4*>(p.out0 + vox * p.ld0 + col) = o[g];
+                else if (col - p.width0 < p.width1) *reinterpret_cast<uint4*>(p.out1 + vox * p.ld1 + (col - p.width0)) = o[g];
               }
             }
           }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty[acc_i]);
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[buf]);
     }
     if (p.stall && threadIdx.x == 96) {
       atomicAdd(&p.stall[4], (unsigned long long)(clock64() - ep_begin));
@@ -288,7 +324,7 @@ __global__ void __launch_bounds__(224, 1) conv_plane3_kernel(const __grid_consta
   if (warp == 0) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
   }
 }
 
@@ -317,7 +353,7 @@ static int cdiv_p3(int a, int b) { return (a + b - 1) / b; }
 // are not multiples of 32, halo or slab operands); the caller then uses the plane-walk kernel.
 int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream) {
   if (a->ksize != 3 || a->W < 16 || a->H < 8 || a->wpack_kd == nullptr) return -1;
-  if (a->cout_pad > 64 || a->cout_pad % 16 != 0) return -1;
+  if (a->cout_pad % 16 != 0 || (a->cout_pad > 64 && a->cout_pad % 64 != 0)) return -1;
   const int cin_tot = a->src_c[0] + a->src_c[1];
   if (a->src_c[0] % P3_BK != 0 || cin_tot % P3_BK != 0) return -1;
   if (a->halo_land[0][0] || a->halo_land[0][1] || a->slab_out[0]) return -1;
@@ -326,26 +362,44 @@ int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream) {
   Plane3Params p;
   memset(&p, 0, sizeof(p));
   const int nsrc = a->src_c[1] > 0 ? 2 : 1;
-  p.BN = a->cout_pad;
+  p.BN = a->cout_pad > 64 ? 64 : a->cout_pad;
   p.N = a->N; p.D = a->D; p.H = a->H; p.W = a->W;
   p.tiles_h = cdiv_p3(a->H, 8);
   p.tiles_w = cdiv_p3(a->W, 16);
-  p.tiles_co = 1;
+  p.tiles_co = a->cout_pad / p.BN;
   p.a_tx = P3_RH * P3_RW * P3_ROWB;
-  p.a_slot_bytes = ((p.a_tx + 1023) / 1024) * 1024;
+  p.a_slot_bytes = ((p.a_tx + 511) / 512) * 512;  // the 64-byte swizzle pattern repeats every 512 bytes
   p.b_tx = 3 * p.BN * P3_ROWB;
   p.b_slot_bytes = ((p.b_tx + 1023) / 1024) * 1024;
-  int td = 4;
-  for (; td > 1; td /= 2) {
-    const long long jobs = (long long)a->N * cdiv_p3(a->D, td) * p.tiles_h * p.tiles_w;
-    if (td <= a->D && 2 * td * p.BN <= 512 && jobs >= 2LL * g_p3_sms) break;
+  // Deep reductions (>= 4 channel blocks) run two CTAs per SM, each with one plane set and one
+  // accumulator buffer: while one CTA's issuing thread sits in a wait, a commit or the turn-around
+  // between channel blocks, the other CTA's MMAs keep the tensor pipe busy (measured: a second
+  // issuing stream hides these gaps). Shallow ones are faster with one CTA per SM that double-buffers
+  // plane sets and accumulators (measured on 64-channel inputs).
+  const bool dual = cin_tot / P3_BK >= 4;
+  const int slots = (dual ? 2 : 1) * g_p3_sms;
+  const int tmem_max = dual ? 256 : 512;
+  p.nsets = dual ? 1 : 2;
+  p.nbufs = dual ? 1 : 2;
+  // Depth of a job: the deepest that keeps the CTA slots busy (last-wave fill x reuse of a weight load).
+  int td = 1;
+  double best = 0.0;
+  for (int cand = 4; cand >= 1; cand /= 2) {
+    const int cols = p.nbufs * cand * p.BN;
+    if (cand > a->D || cols > tmem_max) continue;
+    const long long jobs = (long long)a->N * cdiv_p3(a->D, cand) * p.tiles_h * p.tiles_w * p.tiles_co;
+    const long long waves = (jobs + slots - 1) / slots;
+    const double score = (double)jobs / (double)(waves * slots) * (cand == 4 ? 1.0 : cand == 2 ? 0.93 : 0.8);
+    if (score > best) { best = score; td = cand; }
   }
   p.TD = td;
+  p.tmem_cols = 32;
+  while (p.tmem_cols < p.nbufs * td * p.BN) p.tmem_cols *= 2;
   p.groups_d = cdiv_p3(a->D, td);
-  p.num_jobs = a->N * p.groups_d * p.tiles_h * p.tiles_w;
-  const int budget = g_p3_smem - 1024;
-  const int a_bytes = 2 * (td + 2) * p.a_slot_bytes;
-  int b_slots = (budget - a_bytes) / p.b_slot_bytes;
+  p.num_jobs = a->N * p.groups_d * p.tiles_h * p.tiles_w * p.tiles_co;
+  const int budget = dual ? g_p3_smem / 2 - 2048 : g_p3_smem;  // per CTA
+  const int a_bytes = p.nsets * (td + 2) * p.a_slot_bytes;
+  int b_slots = (budget - 1024 - a_bytes) / p.b_slot_bytes;
   if (b_slots > P3_MAX_B) b_slots = P3_MAX_B;
   if (b_slots < 2) return -1;
   p.b_slots = b_slots;
@@ -375,11 +429,13 @@ int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream) {
   p.ld0 = a->dst_ld[0];
   p.ld1 = a->dst_ld[1];
   if (p.width0 % 8 || p.width1 % 8 || p.ld0 % 8 || p.ld1 % 8) return SB_ERR_SHAPE;
+  p.wide = (p.width0 % 16 == 0 && p.width1 % 16 == 0 && p.ld0 % 16 == 0 && p.ld1 % 16 == 0 &&
+            (reinterpret_cast<uintptr_t>(p.out0) & 31) == 0 && (reinterpret_cast<uintptr_t>(p.out1) & 31) == 0) ? 1 : 0;
   p.bias = a->bias;
   p.status = a->status;
   p.stall = g_p3_stall;
   p.off_d = a->off_d; p.off_h = a->off_h; p.off_w = a->off_w;
-  const int grid = p.num_jobs < g_p3_sms ? p.num_jobs : g_p3_sms;
+  const int grid = p.num_jobs < slots ? p.num_jobs : slots;
   const size_t smem = (size_t)a_bytes + (size_t)p.b_slots * p.b_slot_bytes + 1024;
   if (td == 4) conv_plane3_kernel<4><<<grid, 224, smem, stream>>>(p);
   else if (td == 2) conv_plane3_kernel<2><<<grid, 224, smem, stream>>>(p);

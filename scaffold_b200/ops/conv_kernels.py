@@ -34,8 +34,8 @@ def kd_order(pack: torch.Tensor) -> torch.Tensor:
 
 
 def _attach_kd_order(pack: torch.Tensor) -> torch.Tensor:
-    # narrow outputs (<= 64 rows per tap) run the kd-fused kernel, which wants the second ordering
-    if pack.shape[0] == 27 and pack.shape[1] <= 64 and pack.shape[2] % 32 == 0:
+    # the kd-fused kernel (output channels in tiles of <= 64) wants the second ordering
+    if pack.shape[0] == 27 and (pack.shape[1] <= 64 or pack.shape[1] % 64 == 0) and pack.shape[2] % 32 == 0:
         pack.kd_order = kd_order(pack)
     return pack
 

@@ -46,6 +46,8 @@ FWD_CASES = [
     (2, 7, 24, 48, [64], 64, 3, 4),
     (1, 2, 16, 16, [64, 64], 64, 3, 4),
     (1, 3, 12, 20, [32], 32, 3, 4),
+    (1, 5, 16, 16, [128], 256, 3, 4),
+    (2, 6, 16, 32, [64, 32], 192, 3, 0),
     (1, 9, 16, 16, [32, 96], 48, 3, 0),
     (1, 1, 8, 16, [64], 64, 3, 0),
     (3, 6, 40, 40, [64], 16, 3, 0),
