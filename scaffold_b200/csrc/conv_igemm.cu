@@ -220,43 +220,51 @@ __global__ void __launch_bounds__(192, 1) igemm_kernel(const __grid_constant__ I
         if (valid) {
           const int ngroups = p.BN >= 32 ? 4 : 2;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (g >= ngroups) break;
-            const int col = co0 + ch * 32 + g * 8;
-            float f[8];
+          for (int g2 = 0; g2 < 2; ++g2) {
+            if (g2 * 2 >= ngroups) break;
+            // two groups of 8 channels; they share a destination row when the split points are multiples of 16
+            uint4 o[2];
+            __nv_bfloat16* dst[2] = {nullptr, nullptr};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[g * 8 + j]);
-            __nv_bfloat16* dst = nullptr;
-            if (p.scatter) {
-              const int tap = col / p.sc_cout;
-              const int co = col - tap * p.sc_cout;
-              if (tap < 8) {
-                const int kd = tap >> 2, kh = (tap >> 1) & 1, kw = tap & 1;
-                const long long ov =
-                    (((long long)n * (2 * p.D) + (2 * d + kd)) * (2 * p.H) + (2 * h + kh)) * (2 * p.W) +
-                    (2 * w + kw);
-                dst = p.out0 + ov * p.ld0 + co;
+            for (int gi = 0; gi < 2; ++gi) {
+              const int g = g2 * 2 + gi;
+              const int col = co0 + ch * 32 + g * 8;
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[g * 8 + j]);
+              if (p.scatter) {
+                const int tap = col / p.sc_cout;
+                const int co = col - tap * p.sc_cout;
+                if (tap < 8) {
+                  const int kd = tap >> 2, kh = (tap >> 1) & 1, kw = tap & 1;
+                  const long long ov =
+                      (((long long)n * (2 * p.D) + (2 * d + kd)) * (2 * p.H) + (2 * h + kh)) * (2 * p.W) +
+                      (2 * w + kw);
+                  dst[gi] = p.out0 + ov * p.ld0 + co;
+                  if (p.bias) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) f[j] += p.bias[co + j];
+                  }
+                }
+              } else if (col < p.width0) {
+                dst[gi] = p.out0 + vox * p.ld0 + col;
                 if (p.bias) {
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) f[j] += p.bias[co + j];
+                  for (int j = 0; j < 8; ++j) f[j] += p.bias[col + j];
                 }
+              } else if (col - p.width0 < p.width1) {
+                dst[gi] = p.out1 + vox * p.ld1 + (col - p.width0);
               }
-            } else if (col < p.width0) {
-              dst = p.out0 + vox * p.ld0 + col;
-              if (p.bias) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] += p.bias[col + j];
-              }
-            } else if (col - p.width0 < p.width1) {
-              dst = p.out1 + vox * p.ld1 + (col - p.width0);
+              o[gi].x = pack_bf16x2(f[0], f[1]);
+              o[gi].y = pack_bf16x2(f[2], f[3]);
+              o[gi].z = pack_bf16x2(f[4], f[5]);
+              o[gi].w = pack_bf16x2(f[6], f[7]);
             }
-            if (dst) {
-              uint4 o;
-              o.x = pack_bf16x2(f[0], f[1]);
-              o.y = pack_bf16x2(f[2], f[3]);
-              o.z = pack_bf16x2(f[4], f[5]);
-              o.w = pack_bf16x2(f[6], f[7]);
-              *reinterpret_cast<uint4*>(dst) = o;
+            if (dst[0] && dst[1] == dst[0] + 8 && (reinterpret_cast<uintptr_t>(dst[0]) & 31) == 0) {
+              st_global_v8(dst[0], o[0], o[1]);
+            } else {
+              if (dst[0]) *reinterpret_cast<uint4*>(dst[0]) = o[0];
+              if (dst[1]) *reinterpret_cast<uint4*>(dst[1]) = o[1];
             }
           }
         }
@@ -420,9 +428,11 @@ extern "C" int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream) {
   if (a->force_plain == 0) {
     const int p3 = conv_plane3_launch(a, stream);
     if (p3 >= 0) return p3;
+    if (a->wpack == nullptr) return SB_ERR_SHAPE;  // only the kd-ordered weights were given
     const int prc = conv_plane_launch(a, stream);
     if (prc >= 0) return prc;
   }
+  if (a->wpack == nullptr) return SB_ERR_SHAPE;
   if (a->halo_land[0][0] || a->halo_land[0][1] || a->slab_out[0]) return SB_ERR_SHAPE;  // plane-walk kernel only
   int rc = device_setup();
   if (rc) return rc;

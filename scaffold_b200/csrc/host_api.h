@@ -57,6 +57,18 @@ typedef struct {
   const void* wpack_kd;
 } SbConvArgs;
 
+// One pass over fp32 3x3x3 weights [cout][cin][27] -> bf16 operand layouts (null = not wanted):
+// fwd / fwd_kd [27][cout_pad][cin_pad], dgrad / dgrad_kd [27][cin_pad][cout_pad] (pack.cu).
+// Input channel c goes to column c (c < real0) or c - real0 + pad0 (second concatenated source).
+typedef struct {
+  const float* w;
+  int cout, cin, real0, pad0, cin_pad, cout_pad;
+  void* fwd;
+  void* fwd_kd;
+  void* dgrad;
+  void* dgrad_kd;
+} SbPackArgs;
+
 // k=2,s=2 transposed convolution. Forward: src [N,D,H,W,cin] -> dst
 // [N,2D,2H,2W,cout], wpack bf16 [8*cout][cin] (row = tap*cout + co).
 // Backward-data (sb_convT_dgrad): src = gy [N,2D,2H,2W,cout] -> dst = gx

@@ -56,6 +56,15 @@ class SbConvArgs(C.Structure):
     ]
 
 
+class SbPackArgs(C.Structure):
+    _fields_ = [
+        ("w", C.c_void_p),
+        ("cout", C.c_int), ("cin", C.c_int), ("real0", C.c_int), ("pad0", C.c_int),
+        ("cin_pad", C.c_int), ("cout_pad", C.c_int),
+        ("fwd", C.c_void_p), ("fwd_kd", C.c_void_p), ("dgrad", C.c_void_p), ("dgrad_kd", C.c_void_p),
+    ]
+
+
 class SbConvTArgs(C.Structure):
     _fields_ = [
         ("src", C.c_void_p),
@@ -125,6 +134,7 @@ def lib() -> C.CDLL:
 _P = C.c_void_p
 _SIGNATURES = {
     "sb_conv_fwd": ([C.POINTER(SbConvArgs), _P], C.c_int),
+    "sb_pack_conv3": ([C.POINTER(SbPackArgs), _P], C.c_int),
     "sb_convT_fwd": ([C.POINTER(SbConvTArgs), _P], C.c_int),
     "sb_convT_dgrad": ([C.POINTER(SbConvTArgs), _P], C.c_int),
     "sb_conv_wgrad": ([C.POINTER(SbWgradArgs), _P], C.c_int),

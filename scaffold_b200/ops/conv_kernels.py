@@ -58,6 +58,47 @@ def pack_weight_dgrad(w: torch.Tensor) -> torch.Tensor:
     return _attach_kd_order(out)
 
 
+class Packed:
+    """bf16 operand copies of one 3x3x3 weight for one direction: ``std`` taps in (kd,kh,kw) order and / or
+    ``kd`` taps in (kh,kw,2-kd) order (kd-fused kernel). Shapes ``[27, rows, k]``."""
+    __slots__ = ("std", "kd", "shape")
+
+    def __init__(self, std: Optional[torch.Tensor], kd: Optional[torch.Tensor]):
+        self.std, self.kd = std, kd
+        self.shape = (std if std is not None else kd).shape
+
+
+def kd_eligible(rows: int, k: int, out_dims: Sequence[int], first_src: Optional[int] = None) -> bool:
+    """True when ``sb_conv_fwd`` runs the kd-fused plane kernel for this call (no fused halo / slabs)."""
+    _, h, w = out_dims
+    first = k if first_src is None else first_src
+    return (w >= 16 and h >= 8 and rows % 16 == 0 and (rows <= 64 or rows % 64 == 0) and k % 32 == 0
+            and first % 32 == 0)
+
+
+def pack_conv3(w: torch.Tensor, src_c: Sequence[int], real_c: Sequence[int], want: dict) -> None:
+    """Fill the requested operand layouts of a 3x3x3 weight ``[Cout, Cin, 3,3,3]`` (fp32) in one kernel.
+
+    ``want`` maps 'fwd' / 'fwd_kd' / 'dgrad' / 'dgrad_kd' to zero-initialised bf16 buffers
+    (``[27, cout_pad, cin_pad]`` for forward, ``[27, cin_pad, cout_pad]`` for backward-data); padding
+    positions are never written. ``src_c`` are the (padded) channel counts of the concatenated sources,
+    ``real_c`` the channels of the weight that belong to each.
+    """
+    co, ci = w.shape[:2]
+    a = _lib.SbPackArgs()
+    wc = w.detach().contiguous().float()
+    a.w = wc.data_ptr()
+    a.cout, a.cin = co, ci
+    a.real0, a.pad0 = (real_c[0], src_c[0]) if len(src_c) > 1 else (ci, ci)
+    a.cin_pad, a.cout_pad = sum(src_c), pad_channels(co)
+    if len(src_c) > 2 or (len(src_c) == 2 and real_c[1] > src_c[1]):
+        raise ValueError("pack_conv3 handles at most two concatenated sources")
+    for name in ("fwd", "fwd_kd", "dgrad", "dgrad_kd"):
+        t = want.get(name)
+        setattr(a, name, t.data_ptr() if t is not None else None)
+    _lib.check(_lib.lib().sb_pack_conv3(C.byref(a), _lib.stream_ptr()), "sb_pack_conv3")
+
+
 def pack_weight_convT_fwd(w: torch.Tensor) -> torch.Tensor:
     """[Cin, Cout, 2,2,2] -> bf16 [8*Cout, Cin] (row = tap*Cout + co)."""
     ci, co = w.shape[:2]
@@ -113,9 +154,12 @@ def conv_same(srcs: Sequence[torch.Tensor], wpack: torch.Tensor, ksize: int,
     a.in_d, a.in_h, a.in_w = srcs[0].shape[1:4]
     a.off_d, a.off_h, a.off_w = (int(v) for v in in_off)
     a.ksize = ksize
-    a.wpack = wpack.data_ptr()
+    if isinstance(wpack, Packed):
+        std, kd = wpack.std, (wpack.kd if kd_fused else None)
+    else:
+        std, kd = wpack, (getattr(wpack, "kd_order", None) if kd_fused else None)
+    a.wpack = std.data_ptr() if std is not None else None
     a.cout_pad = wpack.shape[1]
-    kd = getattr(wpack, "kd_order", None) if kd_fused else None
     a.wpack_kd = kd.data_ptr() if kd is not None else None
     if wpack.shape[2] != sum(s.shape[4] for s in srcs):
         raise ValueError(f"packed weight K {wpack.shape[2]} != source channels {[s.shape[4] for s in srcs]}")

@@ -257,3 +257,29 @@ def test_halo_input_conv_fwd_dgrad_wgrad_bitwise(dim, mode):
     ck.conv_wgrad(ndhwc(gy), [ndhwc(x_h)], 3, dw, splits=0 if mode == 0 else -1, x_off=off)
     torch.cuda.synchronize(); _lib.check_status()
     assert torch.equal(dw.double(), wr.grad.round())
+
+
+@pytest.mark.parametrize("shape", [(64, 64, [64], [64]), (48, 3, [16], [3]), (64, 160, [96, 64], [96, 64]),
+                                   (130, 70, [80], [70])], ids=lambda s: f"{s[0]}x{s[1]}")
+def test_fused_weight_pack_matches_torch_packs(shape):
+    """The one-pass packing kernel against the ATen packers, all four layouts."""
+    _lib, ck = _ck()
+    co, ci, src_c, real_c = shape
+    w = torch.randn(co, ci, 3, 3, 3, device="cuda")
+    parts, o = [], 0
+    for sc, rc in zip(src_c, real_c):
+        parts.append(F.pad(w[:, o:o + rc], (0, 0, 0, 0, 0, 0, 0, sc - rc)))
+        o += rc
+    wp = torch.cat(parts, 1)
+    ref_f, ref_d = ck.pack_weight_fwd(wp), ck.pack_weight_dgrad(wp)
+    co_pad, k = ck.pad_channels(co), sum(src_c)
+    want = {"fwd": torch.zeros(27, co_pad, k, dtype=torch.bfloat16, device="cuda"),
+            "fwd_kd": torch.zeros(27, co_pad, k, dtype=torch.bfloat16, device="cuda"),
+            "dgrad": torch.zeros(27, k, co_pad, dtype=torch.bfloat16, device="cuda"),
+            "dgrad_kd": torch.zeros(27, k, co_pad, dtype=torch.bfloat16, device="cuda")}
+    ck.pack_conv3(w, src_c, real_c, want)
+    torch.cuda.synchronize()
+    assert torch.equal(want["fwd"], ref_f)
+    assert torch.equal(want["dgrad"], ref_d)
+    assert torch.equal(want["fwd_kd"], ck.kd_order(ref_f))
+    assert torch.equal(want["dgrad_kd"], ck.kd_order(ref_d))
