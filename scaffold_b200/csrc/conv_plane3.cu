@@ -30,6 +30,7 @@ constexpr int P3_MAX_B = 8;
 struct Plane3Params {
   CUtensorMap mapA[2];
   CUtensorMap mapB;
+  CUtensorMap mapHalo[4];  // [source * 2 + face]: landing slabs of the depth neighbours' boundary planes
   int BN, TD;
   int nsets, nbufs, tmem_cols;  // plane sets / accumulator buffers per CTA (1 when two CTAs share an SM)
   int b_slots, a_slot_bytes, b_slot_bytes, a_tx, b_tx;
@@ -37,6 +38,14 @@ struct Plane3Params {
   int tiles_h, tiles_w, groups_d, tiles_co, num_jobs;
   int cblks, cblks0;
   int off_d, off_h, off_w;
+  int in_D;
+  int halo_has[2];
+  const unsigned* halo_flag[2];
+  unsigned halo_epoch;
+  long long halo_wait_ticks;
+  int slab_mode;
+  __nv_bfloat16* slab_out[2];
+  int slab_ld;
   __nv_bfloat16* out0;
   __nv_bfloat16* out1;
   int width0, width1, ld0, ld1;
@@ -93,6 +102,7 @@ __global__ void __launch_bounds__(224, 2) conv_plane3_kernel(const __grid_consta
       tma_prefetch_desc(&p.mapA[1]);
       uint32_t uses = 0;
       bool ok = true;
+      bool halo_ready[2] = {false, false};
       for (int job = blockIdx.x; job < p.num_jobs && ok; job += gridDim.x) {
         const P3Job jc = p3_decode(p, job);
         for (int cb = 0; cb < p.cblks && ok; ++cb, ++uses) {
@@ -102,10 +112,38 @@ __global__ void __launch_bounds__(224, 2) conv_plane3_kernel(const __grid_consta
           const int second = cb >= p.cblks0 ? 1 : 0;
           const int c = (second ? cb - p.cblks0 : cb) * P3_BK;
           mbar_expect_tx(&a_full[set], (uint32_t)(planes * p.a_tx));
-          for (int j = 0; j < planes; ++j) {
+          for (int j = 0; j < planes && ok; ++j) {
             const int s = set * planes + j;
-            tma_load_5d(smem + (size_t)s * p.a_slot_bytes, &p.mapA[second], &a_full[set], c, jc.h0 - 1 + p.off_h,
-                        jc.w0 - 1 + p.off_w, jc.d0 - 1 + j + p.off_d, jc.n);
+            const int dz = jc.d0 - 1 + j + p.off_d;
+            const int face = dz < 0 ? 0 : (dz >= p.in_D ? 1 : -1);
+            if (face >= 0 && p.halo_has[face]) {
+              // a depth neighbour's boundary plane: wait (bounded) until its push landed, then read it locally
+              if (!halo_ready[face]) {
+                if (p.halo_flag[face] != nullptr) {
+                  const long long t0 = clock64();
+                  uint32_t v;
+                  while (true) {
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.halo_flag[face]) : "memory");
+                    if ((int)(v - p.halo_epoch) >= 0) break;
+                    if (*abort_flag || clock64() - t0 > p.halo_wait_ticks) {
+                      *abort_flag = 1u;
+                      report(p.status, ST_FLAG_TIMEOUT, 77, blockIdx.x, face);
+                      ok = false;
+                      break;
+                    }
+                    __nanosleep(32);
+                  }
+                  if (!ok) break;
+                  asm volatile("fence.proxy.async;" ::: "memory");
+                }
+                halo_ready[face] = true;
+              }
+              tma_load_5d(smem + (size_t)s * p.a_slot_bytes, &p.mapHalo[second * 2 + face], &a_full[set], c,
+                          jc.h0 - 1 + p.off_h, jc.w0 - 1 + p.off_w, 0, jc.n);
+            } else {
+              tma_load_5d(smem + (size_t)s * p.a_slot_bytes, &p.mapA[second], &a_full[set], c, jc.h0 - 1 + p.off_h,
+                          jc.w0 - 1 + p.off_w, dz, jc.n);
+            }
           }
         }
       }
@@ -267,7 +305,15 @@ __global__ void __launch_bounds__(224, 2) conv_plane3_kernel(const __grid_consta
       for (int t = 0; t < TD; ++t) {
         const int d = jc.d0 + t;
         const bool valid = h < p.H && w < p.W && d < p.D;
-        const long long vox = (((long long)jc.n * p.D + d) * p.H + h) * p.W + w;
+        long long vox = (((long long)jc.n * p.D + d) * p.H + h) * p.W + w;
+        __nv_bfloat16* slab = nullptr;
+        if (p.slab_mode) {
+          // output grid = D+2 planes: the two outermost are the halo's gradient and live in slabs
+          if (d == 0) slab = p.slab_out[0];
+          else if (d == p.D - 1) slab = p.slab_out[1];
+          if (slab) vox = ((long long)jc.n * p.H + h) * p.W + w;
+          else vox = (((long long)jc.n * (p.D - 2) + (d - 1)) * p.H + h) * p.W + w;
+        }
         const uint32_t acc_i = buf * TD + t;
         const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + acc_i * p.BN;
         for (int c0 = 0; c0 < p.BN; c0 += 16) {
@@ -282,14 +328,22 @@ __global__ void __launch_bounds__(224, 2) conv_plane3_kernel(const __grid_consta
               float f[8];
 #pragma unroll
               for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[g * 8 + e]);
-              if (p.bias && col0 + g * 8 < p.width0) {
+              if (p.bias && !slab && col0 + g * 8 < p.width0) {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) f[e] += p.bias[col0 + g * 8 + e];
               }
               o[g].x = pack_bf16x2(f[0], f[1]); o[g].y = pack_bf16x2(f[2], f[3]);
               o[g].z = pack_bf16x2(f[4], f[5]); o[g].w = pack_bf16x2(f[6], f[7]);
             }
-            if (p.wide) {
+            if (slab) {
+              if (col0 < p.width0 + p.width1) {
+                if (p.wide) st_global_v8(slab + vox * p.slab_ld + col0, o[0], o[1]);
+                else {
+                  *reinterpret_cast<uint4*>(slab + vox * p.slab_ld + col0) = o[0];
+                  if (col0 + 8 < p.width0 + p.width1) *reinterpret_cast<uint4*>(slab + vox * p.slab_ld + col0 + 8) = o[1];
+                }
+              }
+            } else if (p.wide) {
               // destinations split at a multiple of 16 channels: one 32-byte store per 16 channels
               if (col0 < p.width0) st_global_v8(p.out0 + vox * p.ld0 + col0, o[0], o[1]);
               else if (col0 - p.width0 < p.width1) st_global_v8(p.out1 + vox * p.ld1 + (col0 - p.width0), o[0], o[1]);
@@ -350,13 +404,12 @@ static int p3_setup() {
 static int cdiv_p3(int a, int b) { return (a + b - 1) / b; }
 
 // Returns -1 when the call is not eligible (no kd-grouped weights, wide outputs, channel counts that
-// are not multiples of 32, halo or slab operands); the caller then uses the plane-walk kernel.
+// are not multiples of 32); the caller then uses the plane-walk kernel.
 int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream) {
   if (a->ksize != 3 || a->W < 16 || a->H < 8 || a->wpack_kd == nullptr) return -1;
   if (a->cout_pad % 16 != 0 || (a->cout_pad > 64 && a->cout_pad % 64 != 0)) return -1;
   const int cin_tot = a->src_c[0] + a->src_c[1];
   if (a->src_c[0] % P3_BK != 0 || cin_tot % P3_BK != 0) return -1;
-  if (a->halo_land[0][0] || a->halo_land[0][1] || a->slab_out[0]) return -1;
   int rc = p3_setup();
   if (rc) return rc;
   Plane3Params p;
@@ -435,6 +488,35 @@ int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream) {
   p.status = a->status;
   p.stall = g_p3_stall;
   p.off_d = a->off_d; p.off_h = a->off_h; p.off_w = a->off_w;
+  p.in_D = a->in_d ? a->in_d : a->D;
+  for (int f = 0; f < 2; ++f) {
+    p.halo_has[f] = a->halo_land[0][f] != nullptr ? 1 : 0;
+    p.halo_flag[f] = a->halo_flag[f];
+    for (int sidx = 0; sidx < 2; ++sidx) {
+      const int idx = sidx * 2 + f;
+      if (sidx < nsrc && a->halo_land[sidx][f] != nullptr) {
+        const long long C = a->src_c[sidx];
+        const long long iH = a->in_h ? a->in_h : a->H, iW = a->in_w ? a->in_w : a->W;
+        long long dims[5] = {C, iH, iW, 1, a->N};
+        long long str[5] = {1, iW * C, C, iH * iW * C, iH * iW * C};
+        int box[5] = {P3_BK, P3_RH, P3_RW, 1, 1};
+        rc = make_map_bf16(&p.mapHalo[idx], a->halo_land[sidx][f], 5, dims, str, box, P3_ROWB);
+        if (rc) return rc;
+      } else {
+        p.mapHalo[idx] = p.mapA[0];
+      }
+    }
+  }
+  p.halo_epoch = a->halo_epoch;
+  p.halo_wait_ticks = (long long)((a->halo_wait_s > 0 ? a->halo_wait_s : 2.0) * 1.8e9);
+  p.slab_mode = a->slab_out[0] != nullptr ? 1 : 0;
+  p.slab_out[0] = (__nv_bfloat16*)a->slab_out[0];
+  p.slab_out[1] = (__nv_bfloat16*)a->slab_out[1];
+  p.slab_ld = a->slab_ld;
+  if (p.slab_mode && (p.slab_ld % 8 != 0 || a->D < 3)) return SB_ERR_SHAPE;
+  if (p.slab_mode && (p.slab_ld % 16 != 0 || (reinterpret_cast<uintptr_t>(p.slab_out[0]) & 31) != 0 ||
+                      (reinterpret_cast<uintptr_t>(p.slab_out[1]) & 31) != 0))
+    p.wide = 0;
   const int grid = p.num_jobs < slots ? p.num_jobs : slots;
   const size_t smem = (size_t)a_bytes + (size_t)p.b_slots * p.b_slot_bytes + 1024;
   if (td == 4) conv_plane3_kernel<4><<<grid, 224, smem, stream>>>(p);

@@ -170,7 +170,8 @@ class _ConvHaloFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, weight, bias, mod, chan, *xs):
         src_c = [x.shape[4] for x in xs]
-        wf = mod._cache.conv3(weight, src_c, src_c, "fwd", False)
+        kd = ck.kd_eligible(ck.pad_channels(weight.shape[0]), sum(src_c), xs[0].shape[1:4], src_c[0])
+        wf = mod._cache.conv3(weight, src_c, src_c, "fwd", kd)
         cout_pad = wf.shape[1]
         landing = chan.exchange([x[:, 0] for x in xs], [x[:, -1] for x in xs])
         (y,) = ck.conv_same(list(xs), wf, 3, [cout_pad], halo=landing)
@@ -187,7 +188,8 @@ class _ConvHaloFn(torch.autograd.Function):
         n, d, h, w, _ = gy.shape
         gxs: List[Optional[torch.Tensor]] = [None] * len(xs)
         if any(ctx.needs_input_grad[4 + i] for i in range(len(xs))):
-            wd = mod._cache.conv3(weight, src_c, src_c, "dgrad", False)
+            kd = ck.kd_eligible(sum(src_c), gy.shape[4], (d + 2, h, w))
+            wd = mod._cache.conv3(weight, src_c, src_c, "dgrad", kd)
             ctot = sum(src_c)
             slabs = [torch.empty((n, 1, h, w, ctot), dtype=torch.bfloat16, device=gy.device) for _ in range(2)]
             outs = ck.conv_same([gy], wd, 3, src_c, out_dims=(d + 2, h, w), in_off=(-1, 0, 0), slabs=slabs,
