@@ -89,8 +89,8 @@ def gn_stats(x, w, b, groups, eps, relu, part: Optional[torch.Tensor] = None,
 
 def _set_wait(a: SbGnArgs, wait, device) -> None:
     if wait is not None:
-        a.wait_flags, a.wait_epoch = wait
-        a.wait_s = 2.0
+        a.wait_flags, a.wait_epoch = wait[0], wait[1]
+        a.wait_s = float(wait[2]) if len(wait) > 2 else 2.0  # optional third entry: limit in seconds
         a.status = _lib.status_tensor(device).data_ptr()
 
 

@@ -7,9 +7,15 @@ gradient buffer over all ranks; the optimizer then applies ``1 / ddp_ranks``
 produces in the reference (ScaFFold/worker.py:81-97, ScaFFold/unet/conv3d.py:66-71).
 
 Backends: ``"fused"`` reduces through peer memory with the kernel of
-``csrc/grad_allreduce.cu`` when it is available for the launch, ``"nccl"`` (and
+``csrc/peer.cu`` when it is available for the launch, ``"nccl"`` (and
 every CPU/gloo run) calls ``torch.distributed.all_reduce`` on buckets of the
 flat buffer.
+
+Overlap: on CUDA the flat buffer is cut into buckets in the order backward
+fills it (last layer first). A post-accumulate hook per parameter counts a
+bucket down; when its last gradient has been enqueued the bucket's reduction is
+launched on a side stream behind an event, so it runs under the rest of
+backward. ``reduce()`` launches whatever is left and joins the side stream.
 """
 from __future__ import annotations
 
@@ -20,7 +26,8 @@ import torch.distributed as dist
 
 
 class GradReducer:
-    def __init__(self, layout, flat=None, params=None, backend: str = "nccl", bucket_mb: int = 256):
+    def __init__(self, layout, flat=None, params=None, backend: str = "nccl", bucket_mb: int = 256,
+                 overlap: bool = True, overlap_bucket_mb: int = 32):
         self.layout = layout
         self.flat = flat
         self.params = list(params) if params is not None else None
@@ -37,6 +44,62 @@ class GradReducer:
                 import logging
                 logging.getLogger("scaffold").warning("fused gradient all-reduce unavailable (%s); using NCCL", exc)
                 self._fused = None
+        self._buckets = None
+        self._comm = None
+        if overlap and self.world > 1 and flat is not None and flat.grad.is_cuda:
+            self._setup_overlap(overlap_bucket_mb * (1 << 20) // 4)
+
+    # -- bucketed overlap with backward ---------------------------------------
+    def _setup_overlap(self, bucket_elems: int) -> None:
+        flat = self.flat
+        ends = list(flat.offsets[1:]) + [flat.numel]
+        self._buckets, self._bucket_of = [], {}
+        hi = flat.numel
+        members = []
+        # walk the parameters from the last one (whose gradient arrives first) to the first
+        for i in range(len(flat.params) - 1, -1, -1):
+            members.append(i)
+            lo = flat.offsets[i]
+            if hi - lo >= bucket_elems or i == 0:
+                b = {"lo": lo, "hi": hi, "n": len(members), "pending": len(members), "launched": False}
+                for m in members:
+                    self._bucket_of[id(flat.params[m])] = b
+                self._buckets.append(b)
+                hi, members = lo, []
+        self._comm = torch.cuda.Stream(device=flat.grad.device)
+        self._handles = []
+        for p in flat.params:
+            p.register_post_accumulate_grad_hook(self._on_grad)
+
+    def _on_grad(self, p) -> None:
+        b = self._bucket_of.get(id(p))
+        if b is None or b["launched"]:
+            return
+        b["pending"] -= 1
+        if b["pending"] == 0:
+            self._launch(b)
+
+    def _launch(self, b) -> None:
+        b["launched"] = True
+        ev = torch.cuda.Event()
+        ev.record()
+        with torch.cuda.stream(self._comm):
+            self._comm.wait_event(ev)
+            if self._fused is not None:
+                self._fused.all_reduce_(b["lo"], b["hi"] - b["lo"])
+            else:
+                self._handles.append(dist.all_reduce(self.flat.grad[b["lo"]:b["hi"]], async_op=True))
+
+    def _finish_overlap(self) -> None:
+        for b in self._buckets:
+            if not b["launched"]:  # parameters that received no gradient this step
+                self._launch(b)
+        for h in self._handles:
+            h.wait()
+        self._handles = []
+        torch.cuda.current_stream().wait_stream(self._comm)
+        for b in self._buckets:
+            b["pending"], b["launched"] = b["n"], False
 
     @property
     def scale(self) -> float:
@@ -45,6 +108,9 @@ class GradReducer:
     def reduce(self) -> None:
         """Sum gradients over all ranks (call after backward, before the optimizer step)."""
         if self.world == 1:
+            return
+        if self._buckets is not None:
+            self._finish_overlap()
             return
         if self._fused is not None:
             self._fused.all_reduce_()

@@ -24,7 +24,7 @@ from ..utils.perf import region
 class TrainEngine:
     def __init__(self, model, optimizer, n_classes: int, device, layout=None, spatial=None,
                  class_weights: Optional[torch.Tensor] = None, amp: bool = True, grad_backend: str = "nccl",
-                 max_norm: float = 1.0):
+                 max_norm: float = 1.0, grad_overlap: bool = True):
         self.model, self.optimizer = model, optimizer
         self.n_classes = n_classes
         self.device = torch.device(device)
@@ -35,7 +35,7 @@ class TrainEngine:
         self.cuda = self.device.type == "cuda"
         self.flat = optimizer.attach() if isinstance(optimizer, FusedClipAdam) else None
         params = [p for p in model.parameters() if p.requires_grad]
-        self.reducer = GradReducer(layout, flat=self.flat, params=params, backend=grad_backend)
+        self.reducer = GradReducer(layout, flat=self.flat, params=params, backend=grad_backend, overlap=grad_overlap)
         if isinstance(optimizer, FusedClipAdam):
             optimizer.reduce_scale = self.reducer.scale
         self.last_ce = self.last_dice = None

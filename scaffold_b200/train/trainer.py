@@ -159,7 +159,8 @@ class Trainer:
                                                          float(cfg.ce_weight_sample_fraction), self.log)
         self.engine = TrainEngine(self.model, self.optimizer, self.n_classes, self.device, layout=self.layout,
                                   spatial=self.spatial, class_weights=self.ce_class_weights,
-                                  amp=bool(cfg.torch_amp), grad_backend=getattr(cfg, "grad_allreduce", "nccl"))
+                                  amp=bool(cfg.torch_amp), grad_backend=getattr(cfg, "grad_allreduce", "nccl"),
+                                  grad_overlap=bool(getattr(cfg, "grad_overlap", True)))
 
     # -- reductions -----------------------------------------------------------------
     def _all_reduce_data_parallel(self, t: torch.Tensor) -> None:
