@@ -107,8 +107,7 @@ __global__ void __launch_bounds__(GN_THREADS) gn_stats_kernel(const GnParams p) 
   float shift[8];
   bool have_shift = false;
   if (vl < vpb) {
-    for (long long v = v0 + vl; v < v1; v += vpb) {
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xb + v * p.C));
+    auto body = [&](const uint4 raw) {
       float f[8];
       unpack8(raw, f);
       if (!have_shift) {
@@ -123,7 +122,8 @@ __global__ void __launch_bounds__(GN_THREADS) gn_stats_kernel(const GnParams p) 
         q[i] += d * d;
       }
       cnt += 1.f;
-    }
+    };
+    for (long long v = v0 + vl; v < v1; v += vpb) body(__ldg(reinterpret_cast<const uint4*>(xb + v * p.C)));
   }
   // per-thread (count, mean, M2) for each group it touches (ngt = max(1, 8/cg) groups)
   const int ngt = cg >= 8 ? 1 : 8 / cg;
@@ -231,8 +231,7 @@ __global__ void __launch_bounds__(GN_THREADS) gn_apply_kernel(const GnParams p) 
     c[i] = p.b[ch] - s_mean[g] * a[i];
   }
   const long long base = (long long)n * p.S * p.C + oct * 8;
-  for (long long v = (long long)blockIdx.x * vpb + vl; v < p.S; v += (long long)gridDim.x * vpb) {
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p.x + base + v * p.C));
+  auto body = [&](const uint4 raw, long long v) {
     float f[8];
     unpack8(raw, f);
 #pragma unroll
@@ -242,7 +241,10 @@ __global__ void __launch_bounds__(GN_THREADS) gn_apply_kernel(const GnParams p) 
       f[i] = yv;
     }
     *reinterpret_cast<uint4*>(p.y + base + v * p.C) = pack8(f);
-  }
+  };
+  const long long stride = (long long)gridDim.x * vpb;
+  for (long long v = (long long)blockIdx.x * vpb + vl; v < p.S; v += stride)
+    body(__ldg(reinterpret_cast<const uint4*>(p.x + base + v * p.C)), v);
 }
 
 // ----------------------------------------------------------------------------
@@ -273,9 +275,7 @@ __global__ void __launch_bounds__(GN_THREADS) gn_bwd_partial_kernel(const GnPara
   }
   const long long base = (long long)n * p.S * p.C + oct * 8;
   if (vl < vpb) {
-    for (long long v = v0 + vl; v < v1; v += vpb) {
-      const uint4 rx = __ldg(reinterpret_cast<const uint4*>(p.x + base + v * p.C));
-      const uint4 rd = __ldg(reinterpret_cast<const uint4*>(p.dy + base + v * p.C));
+    auto body = [&](const uint4 rx, const uint4 rd) {
       float fx[8], fd[8];
       unpack8(rx, fx);
       unpack8(rd, fd);
@@ -287,7 +287,20 @@ __global__ void __launch_bounds__(GN_THREADS) gn_bwd_partial_kernel(const GnPara
         A[i] += d;
         B[i] += d * xh;
       }
+    };
+    // two voxels (four 16-byte loads) in flight per thread; the summation order per thread is unchanged
+    long long v = v0 + vl;
+    for (; v + vpb < v1; v += 2 * vpb) {
+      const uint4 rx0 = __ldg(reinterpret_cast<const uint4*>(p.x + base + v * p.C));
+      const uint4 rd0 = __ldg(reinterpret_cast<const uint4*>(p.dy + base + v * p.C));
+      const uint4 rx1 = __ldg(reinterpret_cast<const uint4*>(p.x + base + (v + vpb) * p.C));
+      const uint4 rd1 = __ldg(reinterpret_cast<const uint4*>(p.dy + base + (v + vpb) * p.C));
+      body(rx0, rd0);
+      body(rx1, rd1);
     }
+    for (; v < v1; v += vpb)
+      body(__ldg(reinterpret_cast<const uint4*>(p.x + base + v * p.C)),
+           __ldg(reinterpret_cast<const uint4*>(p.dy + base + v * p.C)));
   }
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -383,9 +396,7 @@ __global__ void __launch_bounds__(GN_THREADS) gn_bwd_dx_kernel(const GnParams p)
     c2[i] = s_c2[g];
   }
   const long long base = (long long)n * p.S * p.C + oct * 8;
-  for (long long v = (long long)blockIdx.x * vpb + vl; v < p.S; v += (long long)gridDim.x * vpb) {
-    const uint4 rx = __ldg(reinterpret_cast<const uint4*>(p.x + base + v * p.C));
-    const uint4 rd = __ldg(reinterpret_cast<const uint4*>(p.dy + base + v * p.C));
+  auto body = [&](const uint4 rx, const uint4 rd, long long v) {
     float fx[8], fd[8];
     unpack8(rx, fx);
     unpack8(rd, fd);
@@ -397,7 +408,21 @@ __global__ void __launch_bounds__(GN_THREADS) gn_bwd_dx_kernel(const GnParams p)
       fx[i] = rs[i] * (d * wv[i] - c1[i] - xh * c2[i]);
     }
     *reinterpret_cast<uint4*>(p.y + base + v * p.C) = pack8(fx);
+  };
+  // two voxels (four 16-byte loads) in flight per thread
+  const long long stride = (long long)gridDim.x * vpb;
+  long long v = (long long)blockIdx.x * vpb + vl;
+  for (; v + stride < p.S; v += 2 * stride) {
+    const uint4 rx0 = __ldg(reinterpret_cast<const uint4*>(p.x + base + v * p.C));
+    const uint4 rd0 = __ldg(reinterpret_cast<const uint4*>(p.dy + base + v * p.C));
+    const uint4 rx1 = __ldg(reinterpret_cast<const uint4*>(p.x + base + (v + stride) * p.C));
+    const uint4 rd1 = __ldg(reinterpret_cast<const uint4*>(p.dy + base + (v + stride) * p.C));
+    body(rx0, rd0, v);
+    body(rx1, rd1, v + stride);
   }
+  for (; v < p.S; v += stride)
+    body(__ldg(reinterpret_cast<const uint4*>(p.x + base + v * p.C)),
+         __ldg(reinterpret_cast<const uint4*>(p.dy + base + v * p.C)), v);
 }
 
 // ----------------------------------------------------------------------------
