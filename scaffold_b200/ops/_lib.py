@@ -135,6 +135,8 @@ _P = C.c_void_p
 _SIGNATURES = {
     "sb_conv_fwd": ([C.POINTER(SbConvArgs), _P], C.c_int),
     "sb_pack_conv3": ([C.POINTER(SbPackArgs), _P], C.c_int),
+    "sb_colsum_blocks": ([], C.c_int),
+    "sb_colsum": ([_P, C.c_longlong, C.c_int, _P, C.c_int, _P, _P], C.c_int),
     "sb_convT_fwd": ([C.POINTER(SbConvTArgs), _P], C.c_int),
     "sb_convT_dgrad": ([C.POINTER(SbConvTArgs), _P], C.c_int),
     "sb_conv_wgrad": ([C.POINTER(SbWgradArgs), _P], C.c_int),

@@ -160,7 +160,7 @@ class _ConvSameFn(torch.autograd.Function):
                     o += sc
                 gw = torch.cat(parts, 1).contiguous()
         if ctx.has_bias and ctx.needs_input_grad[1]:
-            gb = gy.reshape(-1, gy.shape[4]).sum(0, dtype=torch.float32)[: weight.shape[0]]
+            gb = ck.bias_grad(gy, weight.shape[0])
         return (gw, gb, None, None, *gxs)
 
 
@@ -302,7 +302,7 @@ class _ConvTFn(torch.autograd.Function):
             gw = torch.empty_like(weight, dtype=torch.float32)
             ck.conv_wgrad(gy, [x], 2, gw)
         if ctx.has_bias and ctx.needs_input_grad[1]:
-            gb = gy.reshape(-1, gy.shape[4]).sum(0, dtype=torch.float32)
+            gb = ck.bias_grad(gy, gy.shape[4])
         return gw, gb, None, gx
 
 

@@ -99,6 +99,17 @@ def pack_conv3(w: torch.Tensor, src_c: Sequence[int], real_c: Sequence[int], wan
     _lib.check(_lib.lib().sb_pack_conv3(C.byref(a), _lib.stream_ptr()), "sb_pack_conv3")
 
 
+def bias_grad(gy: torch.Tensor, n_out: int) -> torch.Tensor:
+    """fp32 sum of a voxel-major bf16 gradient ``[..., C]`` over all voxels, first ``n_out`` channels."""
+    c = gy.shape[-1]
+    m = gy.numel() // c
+    L = _lib.lib()
+    out = torch.empty(n_out, dtype=torch.float32, device=gy.device)
+    work = torch.empty(L.sb_colsum_blocks() * c, dtype=torch.float32, device=gy.device)
+    _lib.check(L.sb_colsum(gy.data_ptr(), m, c, out.data_ptr(), n_out, work.data_ptr(), _lib.stream_ptr()), "sb_colsum")
+    return out
+
+
 def pack_weight_convT_fwd(w: torch.Tensor) -> torch.Tensor:
     """[Cin, Cout, 2,2,2] -> bf16 [8*Cout, Cin] (row = tap*Cout + co)."""
     ci, co = w.shape[:2]

@@ -127,3 +127,13 @@ def test_unet_forward_backward_close_to_aten():
         mine = (p.grad.float() - q32.grad).abs().max().item() / denom
         lib = (q16.grad.float() - q32.grad).abs().max().item() / denom
         assert mine <= 3.0 * lib + 0.05, (name, mine, lib)
+
+
+@pytest.mark.parametrize("shape", [(2, 4, 8, 16, 64), (1, 3, 5, 7, 16), (1, 16, 16, 16, 512)], ids=str)
+def test_bias_grad_column_sum(shape):
+    from scaffold_b200.ops import conv_kernels as ck
+    g = torch.randn(*shape, device="cuda").to(torch.bfloat16)
+    got = ck.bias_grad(g, shape[-1] - 3)
+    ref = g.double().reshape(-1, shape[-1]).sum(0)[: shape[-1] - 3]
+    torch.testing.assert_close(got.double(), ref, rtol=1e-4, atol=1e-3)
+    assert torch.equal(got, ck.bias_grad(g, shape[-1] - 3))  # fixed summation order
