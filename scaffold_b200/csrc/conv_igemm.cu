@@ -57,7 +57,7 @@ struct IgemmParams {
   uint32_t* status;
 };
 
-__global__ void __launch_bounds__(192, 1) igemm_kernel(const __grid_constant__ IgemmParams p) {
+__global__ void __launch_bounds__(192, 2) igemm_kernel(const __grid_constant__ IgemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t full_bar[MAX_STAGES];
@@ -394,16 +394,21 @@ static int finish_and_launch(IgemmParams& p, int cout_rows, cudaStream_t stream)
   p.a_bytes = ((rows_alloc * rowb + 1023) / 1024) * 1024;
   p.b_bytes = p.KWS * p.KHS * p.BN * rowb;
   p.stage_bytes = ((p.a_bytes + p.b_bytes + 1023) / 1024) * 1024;
-  int st = (g_smem_limit - 1024) / p.stage_bytes;
+  // Two CTAs per SM when there are tiles for them and three stages fit in half the shared memory: the second
+  // CTA's MMAs and epilogue fill the first one's waits (each CTA allocates 256 of the 512 TMEM columns).
+  p.tiles_co = cdiv(cout_rows, p.BN);
+  p.num_tiles = p.tiles_co * p.tiles_w * p.tiles_h * p.tiles_d * p.tiles_n;
+  const int half = g_smem_limit / 2 - 2048;
+  const bool dual = p.num_tiles > g_sm_count && (half - 1024) / p.stage_bytes >= 3;
+  int st = ((dual ? half : g_smem_limit) - 1024) / p.stage_bytes;
   if (st > MAX_STAGES) st = MAX_STAGES;
   if (st < 2) return SB_ERR_SHAPE;
   p.stages = st;
   // expected transaction bytes are what the two boxes really deliver
   p.tx_bytes = rows_a * rowb + p.b_bytes;
-  p.tiles_co = cdiv(cout_rows, p.BN);
-  p.num_tiles = p.tiles_co * p.tiles_w * p.tiles_h * p.tiles_d * p.tiles_n;
   const IgemmParams& q = p;
-  int grid = q.num_tiles < g_sm_count ? q.num_tiles : g_sm_count;
+  const int slots = dual ? 2 * g_sm_count : g_sm_count;
+  int grid = q.num_tiles < slots ? q.num_tiles : slots;
   const size_t smem = (size_t)q.stages * q.stage_bytes + 1024;
   igemm_kernel<<<grid, 192, smem, stream>>>(q);
   sb_count_launch(1);
