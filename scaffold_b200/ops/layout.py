@@ -39,6 +39,15 @@ def use_cuda_kernels(x: torch.Tensor) -> bool:
 
 def to_vm(x: torch.Tensor, pad16: bool = False) -> torch.Tensor:
     """NCDHW-shaped tensor -> contiguous voxel-major bf16 ``[N, D, H, W, C]``."""
+    if (pad16 and x.is_cuda and x.dim() == 5 and x.shape[1] < 16 and x.is_contiguous()
+            and x.dtype in (torch.float32, torch.bfloat16) and not x.requires_grad):
+        # input staging kernel: layout change + down-cast + channel padding in one pass
+        from . import _lib
+        n, c, d, h, w = x.shape
+        y = torch.empty((n, d, h, w, 16), dtype=torch.bfloat16, device=x.device)
+        _lib.check(_lib.lib().sb_stage_input(x.data_ptr(), int(x.dtype == torch.bfloat16), n, c, d * h * w,
+                                             y.data_ptr(), _lib.stream_ptr()), "sb_stage_input")
+        return y
     v = x.permute(0, 2, 3, 4, 1)
     if v.dtype != torch.bfloat16:
         v = v.to(torch.bfloat16)

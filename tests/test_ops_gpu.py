@@ -137,3 +137,12 @@ def test_bias_grad_column_sum(shape):
     ref = g.double().reshape(-1, shape[-1]).sum(0)[: shape[-1] - 3]
     torch.testing.assert_close(got.double(), ref, rtol=1e-4, atol=1e-3)
     assert torch.equal(got, ck.bias_grad(g, shape[-1] - 3))  # fixed summation order
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=str)
+def test_input_staging_kernel_matches_aten(dtype):
+    from scaffold_b200.ops.layout import to_vm
+    x = torch.randn(2, 3, 5, 6, 7, device="cuda").to(dtype)
+    got = to_vm(x, pad16=True)
+    ref = F.pad(x.permute(0, 2, 3, 4, 1).to(torch.bfloat16), (0, 13)).contiguous()
+    assert got.shape == (2, 5, 6, 7, 16) and torch.equal(got, ref)
