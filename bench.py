@@ -191,12 +191,15 @@ def main():
         launches = _lib.launch_count() - launches0
 
         # ---- end-to-end region: pinned-host inputs in, loss value out, every step ----
-        for i in range(2):
-            float(engine.step(*host[i % n_host]).item())
+        # The public training loop: batches come from pinned host memory through the prefetcher (each batch is
+        # copied once, the copy of batch i+1 overlapping step i) and the loss is read back every step.
+        from scaffold_b200.train.prefetch import DevicePrefetcher
+        for batch in DevicePrefetcher([host[i % n_host] for i in range(2)], device):
+            float(engine.step(*batch).item())
         sync()
         e0.record()
-        for i in range(args.steps):
-            loss_val = float(engine.step(*host[i % n_host]).item())
+        for batch in DevicePrefetcher([host[i % n_host] for i in range(args.steps)], device):
+            loss_val = float(engine.step(*batch).item())
         e1.record()
         sync()
         ms_e2e = max_over_ranks(e0.elapsed_time(e1))

@@ -29,6 +29,7 @@ from ..ops.optim import FusedClipAdam
 from ..utils import dist as D
 from ..utils.log import gather_and_print_mem
 from ..utils.perf import adiak_value, begin_code_region, end_code_region, region
+from .prefetch import DevicePrefetcher
 from .checkpoint import CheckpointManager
 from .engine import TrainEngine
 from .evaluate import evaluate
@@ -278,7 +279,7 @@ class Trainer:
                 n_samples, steps, events = 0, 0, []
                 full_batches = self.n_train_local() // int(cfg.local_batch_size)
                 begin_code_region("batch_loop")
-                for bi, batch in enumerate(self.train_loader):
+                for bi, batch in enumerate(DevicePrefetcher(self.train_loader, self.device)):
                     timed = self.device.type == "cuda" and bi < full_batches
                     if timed:
                         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
