@@ -37,7 +37,7 @@ def parse_args():
     ap.add_argument("--bottleneck-dim", type=int, default=3)
     ap.add_argument("--dc-num-shards", type=int, nargs=3, default=[1, 1, 1])
     ap.add_argument("--grad-allreduce", default="fused", choices=["fused", "nccl"])
-    ap.add_argument("--no-grad-overlap", action="store_true", help="reduce gradients in one call after backward")
+    ap.add_argument("--grad-overlap", action="store_true", help="reduce gradient buckets on a side stream during backward")
     ap.add_argument("--halo-exchange", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--gn-stats", default="global", choices=["global", "per_shard"])
     return ap.parse_args()
@@ -145,7 +145,7 @@ def main():
         spatial = SpatialContext(layout, gn_stats=args.gn_stats, halo_backend=args.halo_exchange)
         attach_spatial(model, spatial)
     engine = TrainEngine(model, opt, n_classes, device, layout=layout, spatial=spatial,
-                         grad_backend=args.grad_allreduce, grad_overlap=not args.no_grad_overlap)
+                         grad_backend=args.grad_allreduce, grad_overlap=args.grad_overlap)
 
     S = 2 ** args.scale
     local = [S // n for n in layout.num_shards]  # this rank's sub-volume (D, H, W)
@@ -236,7 +236,7 @@ def main():
             "parallelism": (f"dp{layout.ddp_ranks}" + (f"xsp{sp}{list(layout.num_shards)}" if sp > 1 else "")),
             "batch_per_replica": args.batch,
             "grad_allreduce": args.grad_allreduce if world > 1 else "none",
-            "grad_overlap": bool(world > 1 and not args.no_grad_overlap),
+            "grad_overlap": bool(world > 1 and args.grad_overlap),
             "halo_exchange": args.halo_exchange if sp > 1 else "none",
             "gn_stats": args.gn_stats,
             "l2_policy": "inputs larger than L2 (activations of one step are several GB; two batches rotate)",

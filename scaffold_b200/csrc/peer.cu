@@ -23,7 +23,7 @@
 namespace sb {
 
 constexpr int AR_MAX_RANKS = 8;
-constexpr int AR_THREADS = 512;
+constexpr int AR_THREADS = 256;  // small CTAs co-reside with the persistent convolution CTAs when the reduction overlaps backward
 
 struct AllReduceParams {
   float* bufs[AR_MAX_RANKS];        // every rank's gradient buffer (own entry = local pointer)
@@ -63,7 +63,7 @@ __device__ __forceinline__ bool wait_peers(const AllReduceParams& p, int slot, u
   return __syncthreads_and(ok ? 1 : 0) != 0;
 }
 
-__global__ void __launch_bounds__(AR_THREADS) grad_allreduce_kernel(const AllReduceParams p) {
+__global__ void __launch_bounds__(AR_THREADS, 4) grad_allreduce_kernel(const AllReduceParams p) {
   // phase 0: one CTA announces, every CTA waits on the (local) flag row
   if (blockIdx.x == 0 && threadIdx.x < p.world)
     st_release_sys(p.flags[threadIdx.x] + 0 * AR_MAX_RANKS + p.rank, p.epoch);
@@ -170,7 +170,7 @@ extern "C" int sb_grad_allreduce(void* const* bufs, void* const* flags, int rank
   p.rank = rank; p.world = world; p.offset = offset; p.count = count; p.epoch = epoch; p.scale = scale;
   p.status = status;
   p.wait_ticks = (long long)(wait_seconds * 1.8e9);
-  if (ctas < 1) ctas = 296;
+  if (ctas < 1) ctas = 592;
   grad_allreduce_kernel<<<ctas, AR_THREADS, 0, stream>>>(p);
   sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;

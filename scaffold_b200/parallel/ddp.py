@@ -16,6 +16,9 @@ fills it (last layer first). A post-accumulate hook per parameter counts a
 bucket down; when its last gradient has been enqueued the bucket's reduction is
 launched on a side stream behind an event, so it runs under the rest of
 backward. ``reduce()`` launches whatever is left and joins the side stream.
+Off by default: on 2 and 8 B200s the step time with and without it was the same
+within noise (the reduction is under 5 % of the step and its CTAs compete with
+the persistent convolution kernels for the same SMs).
 """
 from __future__ import annotations
 
@@ -27,7 +30,7 @@ import torch.distributed as dist
 
 class GradReducer:
     def __init__(self, layout, flat=None, params=None, backend: str = "nccl", bucket_mb: int = 256,
-                 overlap: bool = True, overlap_bucket_mb: int = 32):
+                 overlap: bool = False, overlap_bucket_mb: int = 32):
         self.layout = layout
         self.flat = flat
         self.params = list(params) if params is not None else None

@@ -24,7 +24,7 @@ from ..utils.perf import region
 class TrainEngine:
     def __init__(self, model, optimizer, n_classes: int, device, layout=None, spatial=None,
                  class_weights: Optional[torch.Tensor] = None, amp: bool = True, grad_backend: str = "nccl",
-                 max_norm: float = 1.0, grad_overlap: bool = True):
+                 max_norm: float = 1.0, grad_overlap: bool = False):
         self.model, self.optimizer = model, optimizer
         self.n_classes = n_classes
         self.device = torch.device(device)

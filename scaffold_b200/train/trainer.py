@@ -161,7 +161,7 @@ class Trainer:
         self.engine = TrainEngine(self.model, self.optimizer, self.n_classes, self.device, layout=self.layout,
                                   spatial=self.spatial, class_weights=self.ce_class_weights,
                                   amp=bool(cfg.torch_amp), grad_backend=getattr(cfg, "grad_allreduce", "nccl"),
-                                  grad_overlap=bool(getattr(cfg, "grad_overlap", True)))
+                                  grad_overlap=bool(getattr(cfg, "grad_overlap", False)))
 
     # -- reductions -----------------------------------------------------------------
     def _all_reduce_data_parallel(self, t: torch.Tensor) -> None:
