@@ -53,13 +53,17 @@ __global__ void __launch_bounds__(CS_THREADS) colsum_partial_kernel(const __nv_b
   }
 }
 
+// one warp per channel: lanes take the partials b = lane, lane + 32, ... in order, then a fixed shuffle tree
 __global__ void __launch_bounds__(CS_THREADS) colsum_final_kernel(const float* __restrict__ part, int nblocks, int C,
                                                                   float* __restrict__ out, int n_out) {
-  for (int ch = blockIdx.x * CS_THREADS + threadIdx.x; ch < n_out; ch += gridDim.x * CS_THREADS) {
-    float s = 0.f;
-    for (int b = 0; b < nblocks; ++b) s += part[(long long)b * C + ch];
-    out[ch] = s;
-  }
+  const int ch = blockIdx.x * (CS_THREADS / 32) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (ch >= n_out) return;
+  float s = 0.f;
+  for (int b = lane; b < nblocks; b += 32) s += part[(long long)b * C + ch];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) out[ch] = s;
 }
 
 }  // namespace sb
@@ -72,8 +76,8 @@ extern "C" int sb_colsum(const void* x, long long M, int C, float* out, int n_ou
   long long want = (M + rpb - 1) / rpb;
   const int nblocks = (int)(want < 592 ? want : 592);
   sb::colsum_partial_kernel<<<nblocks, sb::CS_THREADS, 0, stream>>>((const __nv_bfloat16*)x, M, C, work);
-  sb::colsum_final_kernel<<<(n_out + sb::CS_THREADS - 1) / sb::CS_THREADS, sb::CS_THREADS, 0, stream>>>(work, nblocks, C,
-                                                                                                     out, n_out);
+  const int cpb = sb::CS_THREADS / 32;
+  sb::colsum_final_kernel<<<(n_out + cpb - 1) / cpb, sb::CS_THREADS, 0, stream>>>(work, nblocks, C, out, n_out);
   sb_count_launch(2);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }

@@ -135,7 +135,7 @@ _P = C.c_void_p
 _SIGNATURES = {
     "sb_conv_fwd": ([C.POINTER(SbConvArgs), _P], C.c_int),
     "sb_pack_conv3": ([C.POINTER(SbPackArgs), _P], C.c_int),
-    "sb_stage_input": ([_P, C.c_int, C.c_int, C.c_int, C.c_longlong, _P, _P], C.c_int),
+    "sb_stage_input": ([_P, C.c_int, C.c_int, C.c_int, C.c_longlong, _P, C.c_int, _P], C.c_int),
     "sb_colsum_blocks": ([], C.c_int),
     "sb_colsum": ([_P, C.c_longlong, C.c_int, _P, C.c_int, _P, _P], C.c_int),
     "sb_convT_fwd": ([C.POINTER(SbConvTArgs), _P], C.c_int),

@@ -98,14 +98,20 @@ class _ConvSameFn(torch.autograd.Function):
     """k in {1,3} stride-1 'same' conv over voxel-major bf16 sources."""
 
     @staticmethod
-    def forward(ctx, weight, bias, mod, in_off, *xs):
+    def forward(ctx, weight, bias, mod, in_off, fwd_xs, *xs):
+        """``xs`` are saved for backward; ``fwd_xs`` (or None) are the same sources padded to more channels,
+        read by the forward kernel only (a few-channel stem runs the kd-fused kernel on 32 padded channels)."""
         ks = weight.shape[2]
         in_off = tuple(int(v) for v in in_off)
         in_dims = tuple(xs[0].shape[1:4])
         out_dims = tuple(d - 2 * o for d, o in zip(in_dims, in_off))
         src_c = [x.shape[4] for x in xs]
         real_c = mod._real_in_channels(src_c)
-        if ks == 3:
+        if fwd_xs is not None:
+            f_src = [x.shape[4] for x in fwd_xs]
+            wf = mod._cache.conv3(weight, f_src, real_c, "fwd",
+                                  ck.kd_eligible(ck.pad_channels(weight.shape[0]), sum(f_src), out_dims, f_src[0]))
+        elif ks == 3:
             kd = ck.kd_eligible(ck.pad_channels(weight.shape[0]), sum(src_c), out_dims, src_c[0])
             wf = mod._cache.conv3(weight, src_c, real_c, "fwd", kd)
         else:
@@ -115,7 +121,8 @@ class _ConvSameFn(torch.autograd.Function):
         bpad = None
         if bias is not None:
             bpad = mod._cache_b.get(bias, "b", lambda b: F.pad(b, (0, cout_pad - b.shape[0])).contiguous())
-        (y,) = ck.conv_same(list(xs), wf, ks, [cout_pad], bias=bpad, out_dims=out_dims, in_off=in_off)
+        (y,) = ck.conv_same(list(fwd_xs if fwd_xs is not None else xs), wf, ks, [cout_pad], bias=bpad,
+                            out_dims=out_dims, in_off=in_off)
         ctx.mod = mod
         ctx.in_off, ctx.in_dims = in_off, in_dims
         ctx.src_c, ctx.real_c = src_c, real_c
@@ -131,7 +138,7 @@ class _ConvSameFn(torch.autograd.Function):
         gy = gy.contiguous()
         src_c, real_c = ctx.src_c, ctx.real_c
         gxs: List[Optional[torch.Tensor]] = [None] * len(xs)
-        need_gx = [ctx.needs_input_grad[4 + i] for i in range(len(xs))]
+        need_gx = [ctx.needs_input_grad[5 + i] for i in range(len(xs))]
         if any(need_gx):
             if ks == 3:
                 # rows = input channels of the layer, K = gy's channels (Cout padded to a multiple of 16)
@@ -147,7 +154,7 @@ class _ConvSameFn(torch.autograd.Function):
                     gxs[i] = o
         gw = gb = None
         if ctx.needs_input_grad[0]:
-            gw = torch.empty_like(weight, dtype=torch.float32)
+            gw = torch.empty(weight.shape, dtype=torch.float32, device=weight.device)  # contiguous whatever the parameter layout
             if list(src_c) == list(real_c):
                 ck.conv_wgrad(gy, list(xs), ks, gw, x_off=ctx.in_off)
             else:
@@ -161,7 +168,7 @@ class _ConvSameFn(torch.autograd.Function):
                 gw = torch.cat(parts, 1).contiguous()
         if ctx.has_bias and ctx.needs_input_grad[1]:
             gb = ck.bias_grad(gy, weight.shape[0])
-        return (gw, gb, None, None, *gxs)
+        return (gw, gb, None, None, None, *gxs)
 
 
 class _ConvHaloFn(torch.autograd.Function):
@@ -203,7 +210,7 @@ class _ConvHaloFn(torch.autograd.Function):
                     gxs[i] = o
         gw = None
         if ctx.needs_input_grad[0]:
-            gw = torch.empty_like(weight, dtype=torch.float32)
+            gw = torch.empty(weight.shape, dtype=torch.float32, device=weight.device)  # contiguous whatever the parameter layout
             ck.conv_wgrad(gy, list(xs), 3, gw, x_halo=ctx.halo_saved)
         return (gw, None, None, None, *gxs)
 
@@ -267,7 +274,13 @@ class Conv3d(nn.Conv3d):
             xs = [sp.halo_pad(t, halo) for t in xs]
             off = tuple(halo if d in sp.dims else 0 for d in (2, 3, 4))
         vms = [to_vm(t, pad16=True) for t in xs]
-        return _ConvSameFn.apply(self.weight, self.bias, self, off, *vms)
+        fwd_vms = None
+        if (len(xs) == 1 and self.kernel_size[0] == 3 and self.in_channels < 16 and not xs[0].requires_grad
+                and vms[0].shape[2] >= 8 and vms[0].shape[3] >= 16):
+            # few input channels (the stem): the forward pass reads a copy padded to 32 channels so that it runs
+            # the kd-fused kernel; the weight gradient keeps the 16-channel copy
+            fwd_vms = (to_vm(xs[0], pad16=True, pad_to=32),)
+        return _ConvSameFn.apply(self.weight, self.bias, self, off, fwd_vms, *vms)
 
     def forward_padded(self, x) -> torch.Tensor:
         """CUDA path only: voxel-major output with the channel axis padded to a multiple of 16."""
@@ -299,7 +312,7 @@ class _ConvTFn(torch.autograd.Function):
             wd = mod._cache.get(weight, "dgrad", ck.pack_weight_convT_dgrad)
             gx = ck.convT_dgrad(gy, wd, x.shape[4])
         if ctx.needs_input_grad[0]:
-            gw = torch.empty_like(weight, dtype=torch.float32)
+            gw = torch.empty(weight.shape, dtype=torch.float32, device=weight.device)  # contiguous whatever the parameter layout
             ck.conv_wgrad(gy, [x], 2, gw)
         if ctx.has_bias and ctx.needs_input_grad[1]:
             gb = ck.bias_grad(gy, gy.shape[4])

@@ -37,23 +37,23 @@ def use_cuda_kernels(x: torch.Tensor) -> bool:
     return torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16
 
 
-def to_vm(x: torch.Tensor, pad16: bool = False) -> torch.Tensor:
+def to_vm(x: torch.Tensor, pad16: bool = False, pad_to: int = 16) -> torch.Tensor:
     """NCDHW-shaped tensor -> contiguous voxel-major bf16 ``[N, D, H, W, C]``."""
     if (pad16 and x.is_cuda and x.dim() == 5 and x.shape[1] < 16 and x.is_contiguous()
             and x.dtype in (torch.float32, torch.bfloat16) and not x.requires_grad):
         # input staging kernel: layout change + down-cast + channel padding in one pass
         from . import _lib
         n, c, d, h, w = x.shape
-        y = torch.empty((n, d, h, w, 16), dtype=torch.bfloat16, device=x.device)
+        y = torch.empty((n, d, h, w, pad_to), dtype=torch.bfloat16, device=x.device)
         _lib.check(_lib.lib().sb_stage_input(x.data_ptr(), int(x.dtype == torch.bfloat16), n, c, d * h * w,
-                                             y.data_ptr(), _lib.stream_ptr()), "sb_stage_input")
+                                             y.data_ptr(), pad_to, _lib.stream_ptr()), "sb_stage_input")
         return y
     v = x.permute(0, 2, 3, 4, 1)
     if v.dtype != torch.bfloat16:
         v = v.to(torch.bfloat16)
     c = v.shape[4]
-    if pad16 and c % 16 != 0:
-        v = F.pad(v, (0, 16 - c % 16))
+    if pad16 and c % pad_to != 0:
+        v = F.pad(v, (0, pad_to - c % pad_to))
     return v.contiguous()
 
 
