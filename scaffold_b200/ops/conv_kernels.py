@@ -291,6 +291,9 @@ def conv_wgrad(gy: torch.Tensor, xs: Sequence[torch.Tensor], ksize: int, dw: tor
     L = _lib.lib()
     need = L.sb_conv_wgrad_workspace(C.byref(a))
     if need < 0:
+        if len(xs) == 2 and x_halo is None:
+            # two narrow sources (below the kernels' 64-channel source tiles): reduce over their concatenation
+            return conv_wgrad(gy, [torch.cat(list(xs), dim=4)], ksize, dw, accumulate, splits, x_off)
         raise _lib.NativeError(f"sb_conv_wgrad: unsupported shape gy={tuple(gy.shape)} xs={[tuple(x.shape) for x in xs]}")
     ws = _workspace(gy.device, need)
     a.workspace, a.workspace_elems = ws.data_ptr(), ws.numel()

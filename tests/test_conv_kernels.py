@@ -283,3 +283,18 @@ def test_fused_weight_pack_matches_torch_packs(shape):
     assert torch.equal(want["dgrad"], ref_d)
     assert torch.equal(want["fwd_kd"], ck.kd_order(ref_f))
     assert torch.equal(want["dgrad_kd"], ck.kd_order(ref_d))
+
+
+def test_wgrad_two_narrow_sources_falls_back_to_their_concatenation():
+    _lib, ck = _ck()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x0, x1 = tri((1, 16, 4, 16, 16), g), tri((1, 16, 4, 16, 16), g)
+    gy = tri((1, 16, 4, 16, 16), g, density=0.3)
+    xcat = torch.cat([x0, x1], 1).double().requires_grad_(False)
+    w = torch.zeros(16, 32, 3, 3, 3, dtype=torch.float64, device="cuda", requires_grad=True)
+    F.conv3d(xcat, w, padding=1).backward(gy.double())
+    dw = torch.empty(16, 32, 3, 3, 3, device="cuda")
+    ck.conv_wgrad(ndhwc(gy), [ndhwc(x0), ndhwc(x1)], 3, dw)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert torch.equal(dw.double(), w.grad.round())

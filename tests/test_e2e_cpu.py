@@ -44,3 +44,12 @@ def test_two_replicas_run_and_resume(tmp_path):
         epochs = [int(r["epoch"]) for r in csv.DictReader(f)]
     assert epochs == [1, 2, 3]  # the first epoch's row survived, training continued at epoch 2
     assert again["epoch1"] == first["epoch1"]
+
+
+def test_device_prefetcher_passes_batches_through_on_cpu():
+    import torch
+    from scaffold_b200.train.prefetch import DevicePrefetcher
+    batches = [{"image": torch.full((1, 2), float(i)), "mask": torch.tensor([i])} for i in range(4)]
+    out = list(DevicePrefetcher(batches, "cpu"))
+    assert len(out) == 4 and all(float(b["image"][0, 0]) == i for i, b in enumerate(out))
+    assert len(DevicePrefetcher(batches, "cpu")) == 4

@@ -36,3 +36,16 @@ def test_two_spatial_shards_match_the_whole_volume_on_gpu(split_dim, halo):
     a, b = (float(v) for v in res["loss"][0].split())
     assert abs(a - b) <= 2e-3 * max(1.0, abs(b)), res
     assert float(res["grad_rel"][0]) < 0.08, res
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("backend", ["fused", "nccl"])
+def test_bucketed_gradient_reduction_under_backward_matches_the_single_call(backend):
+    proc = _torchrun(ROOT / "tests" / "helpers" / "rank_scripts" / "grad_overlap_gpu.py", 2, [backend])
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
+    res = results(proc.stdout)
+    assert res["agree"] == ["True"], res
+    if backend == "fused":  # rank-ordered sums: bitwise the same whatever the bucketing
+        assert res["same"][0].split()[0] == "True", res
+    else:
+        assert float(res["same"][0].split()[1]) < 1e-4, res

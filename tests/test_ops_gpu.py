@@ -146,3 +146,14 @@ def test_input_staging_kernel_matches_aten(dtype):
     got = to_vm(x, pad16=True)
     ref = F.pad(x.permute(0, 2, 3, 4, 1).to(torch.bfloat16), (0, 13)).contiguous()
     assert got.shape == (2, 5, 6, 7, 16) and torch.equal(got, ref)
+
+
+def test_device_prefetcher_delivers_every_batch_once_in_order():
+    from scaffold_b200.train.prefetch import DevicePrefetcher
+    host = [(torch.full((1, 3, 8, 8, 8), float(i)).pin_memory(), torch.full((1, 8, 8, 8), i, dtype=torch.int16).pin_memory())
+            for i in range(5)]
+    seen = []
+    for img, mask in DevicePrefetcher(host, "cuda"):
+        assert img.is_cuda and mask.is_cuda
+        seen.append((float(img.mean()), int(mask.max())))
+    assert seen == [(float(i), i) for i in range(5)]
