@@ -146,6 +146,10 @@ class ConvProblem:
         if self.kernel == 1:
             return "wgrad(generic)" if direction == "wgrad" else "igemm"
         big = w >= 16 and h >= 8
+        rows_, kk_ = (k.cout, k.cin) if direction == "fwd" else (k.cin, k.cout)
+        if (direction != "wgrad" and h == 8 and w == 8 and d % 2 == 0 and 2 <= d <= 8 and rows_ % 128 == 0
+                and not k.split_cin and not any(self.halo)):
+            return "conv_small"
         if direction == "wgrad":
             return "wgrad_plane" if big else "wgrad(generic)"
         rows, kk = (k.cout, k.cin) if direction == "fwd" else (k.cin, k.cout)

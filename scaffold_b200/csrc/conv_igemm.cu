@@ -424,13 +424,22 @@ using namespace sb;
 namespace sb {
 int conv_plane_launch(const SbConvArgs* a, cudaStream_t stream);
 int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream);
+int conv_small_launch(const SbConvArgs* a, cudaStream_t stream);
+long long conv_small_workspace(const SbConvArgs* a);
 }
 
-// force_plain: 0 = automatic (plane-walk kernel when the shape is eligible, else this file's
-// generic kernel), 1 = generic kernel one tap per load, 2 = generic kernel with the w-shift
+// fp32 scratch elements sb_conv_fwd wants for this call (0: none)
+extern "C" long long sb_conv_fwd_workspace(const SbConvArgs* a) {
+  return a->force_plain == 0 ? conv_small_workspace(a) : 0;
+}
+
+// force_plain: 0 = automatic (8 x 8 plane kernel, kd-fused or plane-walk kernel when the shape is eligible, else
+// this file's generic kernel), 1 = generic kernel one tap per load, 2 = generic kernel with the w-shift
 // reuse, 3 = generic kernel with the (h, w)-shift reuse.
 extern "C" int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream) {
   if (a->force_plain == 0) {
+    const int sm = conv_small_launch(a, stream);
+    if (sm >= 0) return sm;
     const int p3 = conv_plane3_launch(a, stream);
     if (p3 >= 0) return p3;
     if (a->wpack == nullptr) return SB_ERR_SHAPE;  // only the kd-ordered weights were given

@@ -55,6 +55,9 @@ typedef struct {
   // Optional second packing of the same 3x3x3 weights, taps ordered (kh, kw, 2-kd): lets the
   // kd-fused kernel (conv_plane3.cu) fetch the three kd taps of a (kh, kw) pair as one box.
   const void* wpack_kd;
+  // fp32 scratch for kernels that split the reduction (conv_small.cu); sb_conv_fwd_workspace() says how much
+  float* workspace;
+  long long workspace_elems;
 } SbConvArgs;
 
 // One pass over fp32 3x3x3 weights [cout][cin][27] -> bf16 operand layouts (null = not wanted):
@@ -156,6 +159,7 @@ int sb_gn_bwd_partial(const SbGnArgs* a, cudaStream_t stream);
 int sb_gn_bwd_dx(const SbGnArgs* a, cudaStream_t stream);
 
 int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream);
+long long sb_conv_fwd_workspace(const SbConvArgs* a);
 int sb_convT_fwd(const SbConvTArgs* a, cudaStream_t stream);
 int sb_convT_dgrad(const SbConvTArgs* a, cudaStream_t stream);
 int sb_conv_wgrad(const SbWgradArgs* a, cudaStream_t stream);

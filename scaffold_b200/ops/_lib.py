@@ -53,6 +53,8 @@ class SbConvArgs(C.Structure):
         ("slab_out", C.c_void_p * 2),
         ("slab_ld", C.c_int),
         ("wpack_kd", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_elems", C.c_longlong),
     ]
 
 
@@ -134,6 +136,7 @@ def lib() -> C.CDLL:
 _P = C.c_void_p
 _SIGNATURES = {
     "sb_conv_fwd": ([C.POINTER(SbConvArgs), _P], C.c_int),
+    "sb_conv_fwd_workspace": ([C.POINTER(SbConvArgs)], C.c_longlong),
     "sb_pack_conv3": ([C.POINTER(SbPackArgs), _P], C.c_int),
     "sb_stage_input": ([_P, C.c_int, C.c_int, C.c_int, C.c_longlong, _P, C.c_int, _P], C.c_int),
     "sb_colsum_blocks": ([], C.c_int),

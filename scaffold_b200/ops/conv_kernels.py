@@ -200,6 +200,10 @@ def conv_same(srcs: Sequence[torch.Tensor], wpack: torch.Tensor, ksize: int,
     if slabs is not None:
         a.slab_out[0], a.slab_out[1] = slabs[0].data_ptr(), slabs[1].data_ptr()
         a.slab_ld = slabs[0].shape[-1]
+    need = _lib.lib().sb_conv_fwd_workspace(C.byref(a))
+    if need > 0:  # kernels that split the reduction keep fp32 partial sums here
+        ws = _workspace(srcs[0].device, need)
+        a.workspace, a.workspace_elems = ws.data_ptr(), ws.numel()
     _lib.check(_lib.lib().sb_conv_fwd(C.byref(a), _lib.stream_ptr()), "sb_conv_fwd")
     return outs
 

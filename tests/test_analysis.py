@@ -52,7 +52,8 @@ def test_conv_problem_cost_model():
     assert p.gemm_shape("wgrad") == (64, 64 * 27, 2 * 128 ** 3)
     assert p.route("fwd") == "conv_plane3" and p.route("wgrad") == "wgrad_plane"
     assert S.ConvProblem(2, 3, 64, (128, 128, 128)).route("fwd") == "conv_plane"   # 16 padded channels
-    assert S.ConvProblem(2, 512, 1024, (8, 8, 8)).route("fwd") == "igemm"
+    assert S.ConvProblem(2, 512, 1024, (8, 8, 8)).route("fwd") == "conv_small"
+    assert S.ConvProblem(2, 64, 128, (4, 4, 4)).route("fwd") == "igemm"
     t = S.ConvProblem(1, 128, 64, (4, 8, 16), 2, True)
     assert t.output_shape == (1, 64, 8, 16, 32) and t.gemm_shape("fwd") == (4 * 8 * 16, 8 * 64, 128)
     h = S.ConvProblem(1, 64, 64, (6, 16, 16), halo=(1, 0, 0))

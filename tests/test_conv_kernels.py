@@ -48,6 +48,9 @@ FWD_CASES = [
     (1, 3, 12, 20, [32], 32, 3, 4),
     (1, 5, 16, 16, [128], 256, 3, 4),
     (2, 6, 16, 32, [64, 32], 192, 3, 0),
+    (2, 8, 8, 8, [64], 128, 3, 0),       # 8 x 8 planes: whole-sample tiles, reduction split over channel blocks
+    (1, 4, 8, 8, [256], 256, 3, 0),
+    (3, 2, 8, 8, [48], 128, 3, 0),
     (1, 9, 16, 16, [32, 96], 48, 3, 0),
     (1, 1, 8, 16, [64], 64, 3, 0),
     (3, 6, 40, 40, [64], 16, 3, 0),
