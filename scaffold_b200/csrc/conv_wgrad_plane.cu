@@ -261,7 +261,24 @@ static int wp_plan(const SbWgradArgs* a, WgradPlaneParams& p) {
   p.Ntot = xc;
   const int base = 3 * p.m_tiles * p.n_tiles;
   const int sms = g_wp_sms > 0 ? g_wp_sms : 148;
-  int splits = a->splits > 0 ? a->splits : sms / base;
+  int splits = a->splits;
+  if (splits <= 0) {
+    // Split count by a small cost model (clock ticks): waves x (blocks per CTA x MMA time per block + epilogue)
+    // + ordered reduce of the partial buffers. It avoids a nearly empty last wave (e.g. 192 CTAs on 148 SMs).
+    const double block_clk = (p.KV / 16) * 2.0 * 96.0;
+    const double epi_clk = 6000.0;
+    const double reduce_clk = 27.0 * gc * xc * 4.0 / 3400.0;
+    double best = 0.0;
+    splits = 1;
+    const int sp_max = 2 * sms / base + 1 > 16 ? 2 * sms / base + 1 : 16;
+    for (int sp = 1; sp <= sp_max && sp <= p.nblocks; ++sp) {
+      const int per = cdiv_wp(p.nblocks, sp);
+      const int eff = cdiv_wp(p.nblocks, per);
+      const int waves = cdiv_wp(base * eff, sms);
+      const double cost = waves * (per * block_clk + epi_clk) + (eff > 1 ? eff * reduce_clk : 0.0);
+      if (sp == 1 || cost < best) { best = cost; splits = eff; }
+    }
+  }
   if (splits < 1) splits = 1;
   if (splits > p.nblocks) splits = p.nblocks;
   p.blocks_per_split = cdiv_wp(p.nblocks, splits);
