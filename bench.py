@@ -194,12 +194,17 @@ def main():
         # The public training loop: batches come from pinned host memory through the prefetcher (each batch is
         # copied once, the copy of batch i+1 overlapping step i) and the loss is read back every step.
         from scaffold_b200.train.prefetch import DevicePrefetcher
+        # The loss of every step is copied to pinned host memory right after the forward pass and read by the host
+        # in the same iteration (engine.read_loss waits for that copy only, not for backward and the update).
+        loss_pin = torch.zeros(1, dtype=torch.float32).pin_memory()
         for batch in DevicePrefetcher([host[i % n_host] for i in range(2)], device):
-            float(engine.step(*batch).item())
+            engine.step(*batch, loss_host=loss_pin)
+            engine.read_loss()
         sync()
         e0.record()
         for batch in DevicePrefetcher([host[i % n_host] for i in range(args.steps)], device):
-            loss_val = float(engine.step(*batch).item())
+            engine.step(*batch, loss_host=loss_pin)
+            loss_val = engine.read_loss()
         e1.record()
         sync()
         ms_e2e = max_over_ranks(e0.elapsed_time(e1))

@@ -39,6 +39,8 @@ class TrainEngine:
         if isinstance(optimizer, FusedClipAdam):
             optimizer.reduce_scale = self.reducer.scale
         self.last_ce = self.last_dice = None
+        self._loss_event = None
+        self._loss_host = None
 
     # -- data movement --------------------------------------------------------
     def to_device(self, images: torch.Tensor, masks: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -77,10 +79,25 @@ class TrainEngine:
             return loss, ce, fg, logits
 
     # -- the step ------------------------------------------------------------------
-    def step(self, images: torch.Tensor, masks: torch.Tensor) -> torch.Tensor:
+    def step(self, images: torch.Tensor, masks: torch.Tensor, loss_host: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One optimizer step; returns the loss as a device scalar.
+
+        ``loss_host`` (a pinned one-element fp32 tensor) receives the loss by an asynchronous copy enqueued right
+        after the forward pass; ``read_loss()`` then returns it without waiting for backward and the update, so a
+        loop that looks at every step's loss does not drain the GPU between steps.
+        """
         images, masks = self.to_device(images, masks)
         self.optimizer.zero_grad(set_to_none=self.flat is None)
         loss, ce, fg, _ = self.forward_loss(images, masks)
+        if loss_host is not None and self.cuda:
+            loss_host.copy_(loss.detach().reshape(loss_host.shape), non_blocking=True)
+            if self._loss_event is None:
+                self._loss_event = torch.cuda.Event()
+            self._loss_event.record()
+            self._loss_host = loss_host
+        elif loss_host is not None:
+            loss_host.copy_(loss.detach().reshape(loss_host.shape))
+            self._loss_host = loss_host
         with region("backward"):
             loss.backward()
         with region("step_and_update"):
@@ -93,6 +110,14 @@ class TrainEngine:
             self.optimizer.step()
         self.last_ce, self.last_dice = ce.detach(), fg.detach()
         return loss.detach()
+
+    def read_loss(self) -> float:
+        """Host value of the loss that the last ``step(..., loss_host=...)`` copied out."""
+        if self._loss_host is None:
+            raise RuntimeError("read_loss() needs a step(..., loss_host=pinned_tensor) before it")
+        if self._loss_event is not None and self.cuda:
+            self._loss_event.synchronize()
+        return float(self._loss_host.reshape(-1)[0])
 
     @torch.no_grad()
     def eval_step(self, images: torch.Tensor, masks: torch.Tensor):

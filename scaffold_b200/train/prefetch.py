@@ -9,34 +9,38 @@ the loader produced. The reference moves each batch synchronously at the top of 
 """
 from __future__ import annotations
 
-from typing import Any, Iterable, Iterator
+from typing import Any, Iterable, Iterator, List
 
 import torch
 
 
-def _to_device(obj: Any, device, stream) -> Any:
+def _flatten(obj: Any, out: List[torch.Tensor]) -> Any:
+    """Replace every tensor by its index in ``out`` (structure is kept for ``_rebuild``)."""
     if torch.is_tensor(obj):
-        t = obj.to(device, non_blocking=True)
-        return t
+        out.append(obj)
+        return ("__tensor__", len(out) - 1)
     if isinstance(obj, dict):
-        return {k: _to_device(v, device, stream) for k, v in obj.items()}
+        return {k: _flatten(v, out) for k, v in obj.items()}
     if isinstance(obj, (list, tuple)):
-        return type(obj)(_to_device(v, device, stream) for v in obj)
+        return type(obj)(_flatten(v, out) for v in obj)
     return obj
 
 
-def _record(obj: Any, stream) -> None:
-    if torch.is_tensor(obj) and obj.is_cuda:
-        obj.record_stream(stream)
-    elif isinstance(obj, dict):
-        for v in obj.values():
-            _record(v, stream)
-    elif isinstance(obj, (list, tuple)):
-        for v in obj:
-            _record(v, stream)
+def _rebuild(spec: Any, tensors: List[torch.Tensor]) -> Any:
+    if isinstance(spec, tuple) and len(spec) == 2 and spec[0] == "__tensor__":
+        return tensors[spec[1]]
+    if isinstance(spec, dict):
+        return {k: _rebuild(v, tensors) for k, v in spec.items()}
+    if isinstance(spec, (list, tuple)):
+        return type(spec)(_rebuild(v, tensors) for v in spec)
+    return spec
 
 
 class DevicePrefetcher:
+    """Two persistent sets of device buffers: batch i+1 is copied into the idle set while step i reads the other.
+    (Fresh allocations per batch on a side stream made the caching allocator fall back to device mallocs.)
+    A yielded batch is valid until the iteration after the next one begins: consume it, do not keep it."""
+
     def __init__(self, batches: Iterable, device):
         self.batches = batches
         self.device = torch.device(device)
@@ -50,20 +54,36 @@ class DevicePrefetcher:
             return
         copy_stream = torch.cuda.Stream(device=self.device)
         it = iter(self.batches)
+        slots: List[List[torch.Tensor]] = [[], []]
+        free_ev = [None, None]  # recorded on the compute stream when the consumer came back for the next batch
 
-        def load():
+        def load(k: int):
             try:
                 host = next(it)
             except StopIteration:
                 return None
+            src: List[torch.Tensor] = []
+            spec = _flatten(host, src)
+            bufs = slots[k]
+            if len(bufs) != len(src) or any(b.shape != t.shape or b.dtype != t.dtype for b, t in zip(bufs, src)):
+                bufs = slots[k] = [torch.empty(t.shape, dtype=t.dtype, device=self.device) for t in src]
+                free_ev[k] = None
             with torch.cuda.stream(copy_stream):
-                return _to_device(host, self.device, copy_stream)
+                if free_ev[k] is not None:
+                    copy_stream.wait_event(free_ev[k])  # the step that read this set has been passed
+                for b, t in zip(bufs, src):
+                    b.copy_(t, non_blocking=True)
+            return _rebuild(spec, bufs)
 
-        nxt = load()
+        k = 0
+        nxt = load(k)
         while nxt is not None:
-            cur = nxt
+            cur, cur_k = nxt, k
             main = torch.cuda.current_stream(self.device)
             main.wait_stream(copy_stream)   # batch i is complete before the step reads it
-            _record(cur, main)              # its memory may be reused only after the step consumed it
-            nxt = load()                    # batch i+1 starts copying under step i
+            k ^= 1
+            nxt = load(k)                   # batch i+1 starts copying under step i
             yield cur
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            free_ev[cur_k] = ev

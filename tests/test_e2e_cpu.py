@@ -53,3 +53,17 @@ def test_device_prefetcher_passes_batches_through_on_cpu():
     out = list(DevicePrefetcher(batches, "cpu"))
     assert len(out) == 4 and all(float(b["image"][0, 0]) == i for i, b in enumerate(out))
     assert len(DevicePrefetcher(batches, "cpu")) == 4
+
+
+def test_engine_copies_the_loss_out_for_the_host():
+    import torch
+    from scaffold_b200.models.unet import UNet
+    from scaffold_b200.train.engine import TrainEngine
+    torch.manual_seed(0)
+    model = UNet(3, 3, layers=1, base_width=8)
+    eng = TrainEngine(model, torch.optim.Adam(model.parameters(), lr=1e-3), 3, "cpu", amp=False)
+    with __import__("pytest").raises(RuntimeError):
+        eng.read_loss()
+    host = torch.zeros(1)
+    loss = eng.step(torch.randn(1, 3, 8, 8, 8), torch.randint(0, 3, (1, 8, 8, 8)), loss_host=host)
+    assert eng.read_loss() == float(loss)
