@@ -249,6 +249,30 @@ __global__ void wgrad_reduce_kernel(const ReduceParams p) {
   p.dw[idx] = acc;
 }
 
+// Same reduction for 3x3x3 weights with the output channel on the workspace's M side (mode 0), through a
+// shared-memory transpose: one block owns (co, 32 input channels): it reads 27 runs of 32 consecutive floats per
+// split (in split order) and writes the 32 x 27 floats that are contiguous in dw[co][ci][tap].
+__global__ void __launch_bounds__(256) wgrad_reduce_t_kernel(const ReduceParams p) {
+  __shared__ float t[27][33];
+  const int co = blockIdx.y, ci0 = blockIdx.x * 32;
+  const size_t slice = (size_t)p.T * p.Mtot * p.Ntot;
+  for (int e = threadIdx.x; e < 27 * 32; e += 256) {
+    const int tap = e >> 5, c = e & 31;
+    const float* src = p.ws + ((size_t)tap * p.Mtot + co) * p.Ntot + ci0 + c;
+    float acc = 0.f;
+    for (int s = 0; s < p.splits; ++s) acc += src[(size_t)s * slice];
+    t[tap][c] = acc;
+  }
+  __syncthreads();
+  float* dst = p.dw + ((size_t)co * p.cin + ci0) * 27;
+  for (int e = threadIdx.x; e < 27 * 32; e += 256) {
+    const int c = e / 27, tap = e - c * 27;
+    float v = t[tap][c];
+    if (p.accumulate) v += dst[e];
+    dst[e] = v;
+  }
+}
+
 static int g_wg_smem = 0, g_wg_sms = 0;
 static int wg_setup() {
   if (g_wg_smem) return 0;
@@ -458,7 +482,10 @@ static int run_reduce(const SbWgradArgs* a, ReduceParams& r, cudaStream_t stream
   r.total = (long long)r.cout * r.cin * r.taps;
   const int threads = 256;
   const long long blocks = (r.total + threads - 1) / threads;
-  wgrad_reduce_kernel<<<(unsigned)blocks, threads, 0, stream>>>(r);
+  if (r.mode == 0 && r.taps == 27 && r.cin % 32 == 0 && r.cout <= 65535)
+    wgrad_reduce_t_kernel<<<dim3(r.cin / 32, r.cout), threads, 0, stream>>>(r);
+  else
+    wgrad_reduce_kernel<<<(unsigned)blocks, threads, 0, stream>>>(r);
   sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }
