@@ -87,7 +87,7 @@ class ClockSampler:
 
 
 def baseline_value():
-    """BASELINE.md publishes no end-to-end throughput, so there is nothing to divide by."""
+    """The reference publishes no voxels-per-second figure for this configuration, so there is nothing to divide by."""
     return None
 
 
