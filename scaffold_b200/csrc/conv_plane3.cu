@@ -32,6 +32,7 @@ struct Plane3Params {
   CUtensorMap mapB;
   CUtensorMap mapHalo[4];  // [source * 2 + face]: landing slabs of the depth neighbours' boundary planes
   int BN, TD;
+  int bgroup;  // (kh,kw) pairs per weight box: 1, or 3 (a whole kh row, fewer waits) when shared memory allows
   int nsets, nbufs, tmem_cols;  // plane sets / accumulator buffers per CTA (1 when two CTAs share an SM)
   int b_slots, a_slot_bytes, b_slot_bytes, a_tx, b_tx;
   int N, D, H, W;
@@ -157,7 +158,7 @@ __global__ void __launch_bounds__(224, 2) conv_plane3_kernel(const __grid_consta
       for (int job = blockIdx.x; job < p.num_jobs && ok; job += gridDim.x) {
         const P3Job jc = p3_decode(p, job);
         for (int cb = 0; cb < p.cblks && ok; ++cb) {
-          for (int khw = 0; khw < 9; ++khw, ++it) {
+          for (int khw = 0; khw < 9; khw += p.bgroup, ++it) {
             const int s = it % p.b_slots;
             const uint32_t ph = (it / p.b_slots) & 1u;
             if (!mbar_wait(&b_empty[s], ph ^ 1u, abort_flag, p.status, 72)) { ok = false; break; }
@@ -212,7 +213,9 @@ __global__ void __launch_bounds__(224, 2) conv_plane3_kernel(const __grid_consta
         for (int khw = 0; khw < 9; ++khw) {
           const int kh = khw / 3, kw = khw - kh * 3;
           tc_fence_after();
-          const uint32_t b_lo0 = desc_lo(sb0 + b_slot * (uint32_t)p.b_slot_bytes, 16u);
+          const int sub = p.bgroup == 3 ? kw : 0;             // position of this (kh,kw) pair inside its weight box
+          const bool box_done = p.bgroup == 3 ? kw == 2 : true;  // last pair of the box: the next step reads a new slot
+          const uint32_t b_lo0 = desc_lo(sb0 + b_slot * (uint32_t)p.b_slot_bytes, 16u) + (uint32_t)sub * 3u * b_tap;
           const uint32_t a_tap = a_set + (((uint32_t)(kw * P3_RH + kh) * P3_ROWB) >> 4);
           const bool first = (cb | khw) == 0;
           uint32_t nb_slot = b_slot + 1, nb_par = b_par;
@@ -251,7 +254,7 @@ __global__ void __launch_bounds__(224, 2) conv_plane3_kernel(const __grid_consta
               // look ahead: what the next step reads
               const bool more = !(last_job && last_cb && khw == 8);
               if (more) {
-                if (!P3_WAIT(st_b, &b_full[nb_slot], nb_par, 73)) { ok = false; break; }
+                if (box_done && !P3_WAIT(st_b, &b_full[nb_slot], nb_par, 73)) { ok = false; break; }
                 if (khw == 8) {
                   const uint32_t nu = uses + 1;
                   if (sets2 && !P3_WAIT(st_a, &a_full[nu & 1u], (nu >> 1) & 1u, 74)) { ok = false; break; }
@@ -265,15 +268,17 @@ __global__ void __launch_bounds__(224, 2) conv_plane3_kernel(const __grid_consta
           }
           if (!ok) break;
           if (leader) {
-            tc_commit(&b_empty[b_slot]);
+            if (box_done) tc_commit(&b_empty[b_slot]);
             if (khw == 8) {
               tc_commit(&set_empty[set]);
               if (last_cb) tc_commit(&tfull[buf]);
             }
           }
           __syncwarp();
-          b_slot = nb_slot;
-          b_par = nb_par;
+          if (box_done) {
+            b_slot = nb_slot;
+            b_par = nb_par;
+          }
         }
       }
     }
@@ -422,8 +427,6 @@ int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream) {
   p.tiles_co = a->cout_pad / p.BN;
   p.a_tx = P3_RH * P3_RW * P3_ROWB;
   p.a_slot_bytes = ((p.a_tx + 511) / 512) * 512;  // the 64-byte swizzle pattern repeats every 512 bytes
-  p.b_tx = 3 * p.BN * P3_ROWB;
-  p.b_slot_bytes = ((p.b_tx + 1023) / 1024) * 1024;
   // Deep reductions (>= 4 channel blocks) run two CTAs per SM, each with one plane set and one
   // accumulator buffer: while one CTA's issuing thread sits in a wait, a commit or the turn-around
   // between channel blocks, the other CTA's MMAs keep the tensor pipe busy (measured: a second
@@ -452,7 +455,14 @@ int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream) {
   p.num_jobs = a->N * p.groups_d * p.tiles_h * p.tiles_w * p.tiles_co;
   const int budget = dual ? g_p3_smem / 2 - 2048 : g_p3_smem;  // per CTA
   const int a_bytes = p.nsets * (td + 2) * p.a_slot_bytes;
-  int b_slots = (budget - 1024 - a_bytes) / p.b_slot_bytes;
+  // weight boxes of a whole kh row (nine taps) when two of them fit: a third of the waits and commits
+  int b_slots = 0;
+  for (p.bgroup = 3; p.bgroup >= 1; p.bgroup -= 2) {
+    p.b_tx = 3 * p.bgroup * p.BN * P3_ROWB;
+    p.b_slot_bytes = ((p.b_tx + 1023) / 1024) * 1024;
+    b_slots = (budget - 1024 - a_bytes) / p.b_slot_bytes;
+    if (b_slots >= 2) break;
+  }
   if (b_slots > P3_MAX_B) b_slots = P3_MAX_B;
   if (b_slots < 2) return -1;
   p.b_slots = b_slots;
@@ -471,7 +481,7 @@ int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream) {
   {
     long long dims[3] = {cin_tot, a->cout_pad, 27};
     long long str[3] = {1, cin_tot, (long long)a->cout_pad * cin_tot};
-    int box[3] = {P3_BK, p.BN, 3};
+    int box[3] = {P3_BK, p.BN, 3 * p.bgroup};
     rc = make_map_bf16(&p.mapB, a->wpack_kd, 3, dims, str, box, P3_ROWB);
     if (rc) return rc;
   }
