@@ -40,12 +40,41 @@ __global__ void __launch_bounds__(256) pack_conv3_kernel(SbPackArgs a) {
   const int co0 = blockIdx.x * PK_T, ci0 = blockIdx.y * PK_T;
   const int nco = min(PK_T, a.cout - co0), nci = min(PK_T, a.cin - ci0);
   const int run = nci * 27;
-  for (int i = threadIdx.x; i < PK_T * PK_T * 27; i += blockDim.x) {
-    const int r = i / (PK_T * 27), j = i - r * (PK_T * 27);
-    const int ci = j / 27, tap = j - ci * 27;
-    float v = 0.f;
-    if (r < nco && j < run) v = a.w[((long long)(co0 + r) * a.cin + ci0) * 27 + j];
-    tile[tap * PK_PLANE + r * PK_LD + ci] = __float2bfloat16(v);
+  if (nci == PK_T && (a.cin % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.w) & 15) == 0)) {
+    // full tile: each row is 864 contiguous floats starting on a 16-byte boundary; 16-byte loads, two in flight
+    constexpr int V = PK_T * 27 / 4;  // float4 per row
+    for (int i = threadIdx.x; i < PK_T * V; i += 2 * blockDim.x) {
+      float4 v[2];
+      int rr[2], jj[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int iu = i + u * blockDim.x;
+        rr[u] = iu / V;
+        jj[u] = (iu - rr[u] * V) * 4;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (iu < PK_T * V && rr[u] < nco)
+          v[u] = __ldg(reinterpret_cast<const float4*>(a.w + ((long long)(co0 + rr[u]) * a.cin + ci0) * 27 + jj[u]));
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (i + u * blockDim.x >= PK_T * V) continue;
+        const float e[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int j = jj[u] + q;
+          const int ci = j / 27, tap = j - ci * 27;
+          tile[tap * PK_PLANE + rr[u] * PK_LD + ci] = __float2bfloat16(e[q]);
+        }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < PK_T * PK_T * 27; i += blockDim.x) {
+      const int r = i / (PK_T * 27), j = i - r * (PK_T * 27);
+      const int ci = j / 27, tap = j - ci * 27;
+      float v = 0.f;
+      if (r < nco && j < run) v = a.w[((long long)(co0 + r) * a.cin + ci0) * 27 + j];
+      tile[tap * PK_PLANE + r * PK_LD + ci] = __float2bfloat16(v);
+    }
   }
   __syncthreads();
   // Where the tile's 32 input channels land: contiguous unless the tile straddles the end of a padded source.
