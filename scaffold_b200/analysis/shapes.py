@@ -232,3 +232,34 @@ def summarize(problems: Sequence[ConvProblem]) -> Dict[str, float]:
             total[d] += p.roofline_seconds(d) * 1e3
     total["all"] = sum(total.values())
     return total
+
+
+def main(argv=None) -> int:
+    """``python -m scaffold_b200.analysis.shapes [--problem-scale 7 --batch 2 --dc-num-shards 2 1 1]``: the corpus
+    of one configuration with FLOPs, arithmetic intensity, roofline time and the kernel each direction runs on."""
+    import argparse
+    ap = argparse.ArgumentParser(description="Convolution corpus of a U-Net configuration with roofline and routing")
+    ap.add_argument("--problem-scale", type=int, default=7)
+    ap.add_argument("--unet-bottleneck-dim", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--n-categories", type=int, default=8)
+    ap.add_argument("--base-width", type=int, default=64)
+    ap.add_argument("--dc-num-shards", type=int, nargs=3, default=[1, 1, 1])
+    a = ap.parse_args(argv)
+    tf, gbs, which = measured_peaks()
+    print(f"roofs ({which}): {tf:.0f} TFLOP/s bf16, {gbs:.0f} GB/s")
+    probs = scaffold_corpus(a.problem_scale, a.unet_bottleneck_dim, a.batch, a.n_categories, a.base_width,
+                            tuple(a.dc_num_shards))
+    print(f"{'layer':34s} {'problem':40s} {'GFLOP':>8s} {'AI':>7s} {'roof ms':>8s}  fwd / dgrad / wgrad kernels")
+    for p in probs:
+        print(f"{p.name:34s} {p.label:40s} {p.flops() / 1e9:8.1f} {p.arithmetic_intensity():7.0f} "
+              f"{p.roofline_seconds() * 1e3:8.3f}  {p.route('fwd')} / {p.route('dgrad')} / {p.route('wgrad')}")
+    tot = summarize(probs)
+    print(f"roofline of one step's convolutions: fwd {tot['fwd']:.2f} + dgrad {tot['dgrad']:.2f} + wgrad "
+          f"{tot['wgrad']:.2f} = {tot['all']:.2f} ms")
+    return 0
+
+
+if __name__ == "__main__":
+    import sys
+    sys.exit(main())

@@ -109,3 +109,10 @@ def test_restart_script_rewrites_argv():
                    "$RUN_DIR"]
     text = restart_script.render(Path("/tmp/r"), ["benchmark", "-c", "a.yml"])
     assert 'RUN_DIR="$(cd' in text and "--restart --run-dir $RUN_DIR" in text
+
+
+def test_grad_overlap_key_and_flag(tmp_path):
+    merged = C.load_config_files([str(C.default_config_path())])
+    assert C.Config(dict(merged, base_run_dir=str(tmp_path))).grad_overlap is False
+    args = cli.build_parser().parse_args(["benchmark", "--grad-overlap", "1"])
+    assert "grad_overlap" in cli.explicit_cli_keys(args) and args.grad_overlap == 1
