@@ -29,12 +29,12 @@ def run(args):
         return {"impl": "reference", "unavailable": "baseline/_ref is empty (offline install not done on this box)"}
     os.environ.setdefault("SCAFFOLD_GROUPNORM_TRITON", "1")
     sys.path.insert(0, str(REF))
-    import json
     import torch
     import torch.distributed as dist
     import torch.nn.functional as F
 
     from ScaFFold.unet.unet_model import UNet  # noqa: E402
+    from baseline.common_config import workload_config  # noqa: E402
     from ScaFFold.utils.dice_score import compute_sharded_dice, labels_to_onehot  # noqa: E402
     from ScaFFold.utils.losses import compute_sharded_cross_entropy_loss  # noqa: E402
 
@@ -131,11 +131,11 @@ def run(args):
         "ms_per_step": ms_total / args.steps,
         "higher_is_better": True, "scaling": "weak", "dtype": "bf16",
         "data": "synthetic (random volumes and labels of the dataset's shape; random-init weights)",
-        "config": {"model": f"reference UNet scale {args.scale}: {layers + 1} levels, base width 64, GroupNorm(8), "
-                            f"{n_classes} classes", "global_batch": args.batch * world, "seq_len": S ** 3,
-                   "parallelism": f"dp{world}", "final_loss": loss_val,
-                   "kernels": "cuDNN conv (cudnn.benchmark), Triton GroupNorm (SCAFFOLD_GROUPNORM_TRITON=1), "
-                              "torch DDP/NCCL, fused Adam"},
+        "config": workload_config(args.scale, layers + 1, 64, n_classes, sum(p.numel() for p in model.parameters()),
+                                  args.batch, world, [1, 1, 1],
+                                  {"final_loss": loss_val,
+                                   "kernels": "cuDNN conv (cudnn.benchmark), Triton GroupNorm "
+                                              "(SCAFFOLD_GROUPNORM_TRITON=1), torch DDP/NCCL, fused Adam"}),
         "e2e": {"value": vox / (ms_e2e / args.steps / 1e3), "unit": "voxels/s",
                 "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host[0]), "d2h_bytes_per_step": 4},

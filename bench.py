@@ -112,7 +112,9 @@ def main():
 
     from scaffold_b200.models.unet import UNet
     from scaffold_b200.ops import _lib
+    from baseline.common_config import workload_config
     from scaffold_b200.ops.optim import FusedClipAdam
+    from scaffold_b200.ops.selection import effective_backends
     from scaffold_b200.parallel.layout import ParallelLayout
     from scaffold_b200.parallel.spatial import SpatialContext
     from scaffold_b200.run import attach_spatial
@@ -232,21 +234,15 @@ def main():
         "dtype": "bf16",
         "data": "synthetic (random volumes and labels of the dataset's shape; random-init weights)",
         "impl": "ours",
-        "config": {
-            "model": f"3D U-Net scale {args.scale}: {layers + 1} levels, base width {args.base_width}, GroupNorm(8), "
-                     f"{n_classes} classes, {sum(p.numel() for p in model.parameters())} params",
-            "global_batch": global_batch,
-            "seq_len": S ** 3,
-            "volume": [S, S, S],
-            "parallelism": (f"dp{layout.ddp_ranks}" + (f"xsp{sp}{list(layout.num_shards)}" if sp > 1 else "")),
-            "batch_per_replica": args.batch,
-            "grad_allreduce": args.grad_allreduce if world > 1 else "none",
-            "grad_overlap": bool(world > 1 and args.grad_overlap),
-            "halo_exchange": args.halo_exchange if sp > 1 else "none",
-            "gn_stats": args.gn_stats,
-            "l2_policy": "inputs larger than L2 (activations of one step are several GB; two batches rotate)",
-            "final_loss": loss_val,
-        },
+        "config": workload_config(args.scale, layers + 1, args.base_width, n_classes,
+                                  sum(p.numel() for p in model.parameters()), args.batch, layout.ddp_ranks,
+                                  layout.num_shards,
+                                  {"final_loss": loss_val,
+                                   "kernels": "sm_100a tcgen05/TMA kernels of libscaffold_b200.so (conv, GroupNorm, "
+                                              "pool, loss, Adam); peer-memory collectives",
+                                   "grad_allreduce_requested": args.grad_allreduce if world > 1 else "none",
+                                   "halo_exchange_requested": args.halo_exchange if sp > 1 else "none",
+                                   "gn_stats": args.gn_stats, **effective_backends(engine)}),
         "clocks": clocks.summary(),
         "e2e": {"value": e2e_value, "unit": "voxels/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},

@@ -37,7 +37,7 @@ BENCHMARK_FLAGS = {
     "--target-dice": ("target_dice", float), "--checkpoint-interval": ("checkpoint_interval", int),
     "--unet-base-width": ("unet_base_width", int), "--gn-stats": ("gn_stats", str),
     "--grad-allreduce": ("grad_allreduce", str), "--halo-exchange": ("halo_exchange", str),
-    "--grad-overlap": ("grad_overlap", int),
+    "--grad-overlap": ("grad_overlap", int), "--allow-fallback": ("allow_fallback", int),
 }
 GENERATE_FLAGS = {
     "--datagen-batch-size": ("datagen_batch_size", int), "--problem-scale": ("problem_scale", int),

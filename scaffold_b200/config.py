@@ -134,6 +134,7 @@ SCHEMA: List[Key] = [
     Key("grad_allreduce", "fused", conv=_choice("fused", "nccl")),
     Key("grad_overlap", False, conv=_flag),
     Key("halo_exchange", "fused", conv=_choice("fused", "nccl")),
+    Key("allow_fallback", False, conv=_flag),
     Key("point_num_override", None, scalar=True),
     Key("datagen_device", "auto", conv=_choice("auto", "cpu", "cuda")),
 ]

@@ -486,11 +486,20 @@ __global__ void __launch_bounds__(GN_THREADS) gn_bwd_finalize_kernel(const float
   }
 }
 
+// Channel / group counts the kernels cover: C a multiple of 8 in [8, 2048] (one thread per channel
+// octet, at most GN_THREADS octets), G dividing C, and a group either a whole number of octets or a
+// divisor of one octet holding at most four groups.
+static bool gn_channels_ok(int C, int G) {
+  if (C < 8 || C % 8 != 0 || C > 8 * GN_THREADS || G < 1 || G > 256 || C % G != 0) return false;
+  const int cg = C / G;
+  if (cg < 8 ? (8 % cg != 0) : (cg % 8 != 0)) return false;
+  return !(cg < 8 && 8 / cg > 4);
+}
+
 static int gn_fill(const SbGnArgs* a, GnParams& p) {
-  if (a->C % 8 != 0 || a->C % a->G != 0 || a->C > 2048 || a->G > 256) return SB_ERR_SHAPE;
+  if (!gn_channels_ok(a->C, a->G) || a->N < 1 || a->S < 1) return SB_ERR_SHAPE;
+  if (a->x == nullptr || a->w == nullptr || a->b == nullptr) return SB_ERR_SHAPE;
   const int cg = a->C / a->G;
-  if (cg < 8 ? (8 % cg != 0) : (cg % 8 != 0)) return SB_ERR_SHAPE;
-  if (a->C / 8 > GN_THREADS || (cg < 8 && 8 / cg > 4)) return SB_ERR_SHAPE;
   if (a->n_parts < 1 || a->n_parts > GN_MAX_PARTS) return SB_ERR_SHAPE;
   memset(&p, 0, sizeof(p));
   p.x = (const __nv_bfloat16*)a->x;
@@ -525,7 +534,11 @@ static int apply_blocks(const GnParams& p) {
 
 using namespace sb;
 
+// 1 when the kernels cover GroupNorm over C channels in G groups, else 0 (callers then take another path)
+extern "C" int sb_gn_supported(int C, int G) { return gn_channels_ok(C, G) ? 1 : 0; }
+
 extern "C" int sb_gn_nsplit(int N, long long S, int C) {
+  if (N < 1 || S < 1 || C < 8 || C / 8 > GN_THREADS) return 1;  // unsupported shapes are refused by the launchers
   const int vpb = GN_THREADS / (C / 8);
   long long maxs = (S + vpb - 1) / vpb;  // at least one row of voxels per split
   long long want = (148LL * 4 + N - 1) / N;
@@ -636,7 +649,8 @@ static float* g_gn_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
 extern "C" int sb_gn_forward_noalloc(const void* x, void* y, const float* w, const float* b, float* mean,
                                      float* rstd, int N, long long S, int C, int G, float eps, int relu,
                                      cudaStream_t stream) {
-  if (N < 1 || N > 64 || G < 1 || G > 256) return SB_ERR_SHAPE;
+  if (N < 1 || N > 64 || S < 1 || !gn_channels_ok(C, G)) return SB_ERR_SHAPE;
+  if (x == nullptr || y == nullptr || w == nullptr || b == nullptr) return SB_ERR_SHAPE;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return SB_ERR_DRIVER;
   if (g_gn_noalloc_ptr[dev] == nullptr) {

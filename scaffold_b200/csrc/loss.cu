@@ -17,6 +17,11 @@
 //   dL/dp_c(v) = alpha[n][c] * [y(v)=c] + beta[n][c] and k_ce = g / denominator:
 //     dlogit_j = k_ce * w[y] * (p_j - [y=j]) + p_j * (a_j - sum_c a_c p_c)
 //
+// A label outside [0, C) (a dataset with more categories than the model, an ignore
+// value) is never used as an index: the voxel gets weight 0 in the cross entropy and
+// belongs to no class in the Dice sums, and the kernels record ST_BAD_ARG (site 61 /
+// 62, detail = label value) in the status word so that the host can raise.
+//
 // Role of the reference: ScaFFold/utils/trainer.py:635-664,
 // ScaFFold/utils/losses.py:117-205, ScaFFold/utils/dice_score.py:101-136,
 // ScaFFold/utils/evaluate.py:178-193.
@@ -88,7 +93,8 @@ template <int CP>
 __global__ void __launch_bounds__(LOSS_THREADS) loss_sums_kernel(const __nv_bfloat16* __restrict__ logits,
                                                                  const void* __restrict__ labels, int label_kind,
                                                                  const float* __restrict__ cw, float* __restrict__ ws,
-                                                                 int C, long long S, int argmax_mode) {
+                                                                 int C, long long S, int argmax_mode,
+                                                                 uint32_t* __restrict__ status) {
   __shared__ float red[LOSS_THREADS / 32];
   const int n = blockIdx.y;
   float P[CP], Q[CP], I[CP];
@@ -99,7 +105,10 @@ __global__ void __launch_bounds__(LOSS_THREADS) loss_sums_kernel(const __nv_bflo
        v += (long long)gridDim.x * LOSS_THREADS) {
     float f[CP];
     load_logits<CP>(logits + ((long long)n * S + v) * CP, f);
-    const int y = (int)load_label(labels, label_kind, (long long)n * S + v);
+    const long long y_raw = load_label(labels, label_kind, (long long)n * S + v);
+    const bool y_ok = y_raw >= 0 && y_raw < C;
+    const int y = y_ok ? (int)y_raw : -1;
+    if (!y_ok) report(status, ST_BAD_ARG, 61, (uint32_t)y_raw, (uint32_t)n);
     float ly = 0.f;
 #pragma unroll
     for (int c = 0; c < CP; ++c)
@@ -120,7 +129,7 @@ __global__ void __launch_bounds__(LOSS_THREADS) loss_sums_kernel(const __nv_bflo
       P[c] += f[c];
       if (c == y) { Q[c] += 1.f; I[c] += f[c]; }
     }
-    const float wy = cw ? cw[y] : 1.f;
+    const float wy = y_ok ? (cw ? cw[y] : 1.f) : 0.f;
     ce_num += wy * (lse - ly);
     ce_den += wy;
   }
@@ -159,7 +168,7 @@ __global__ void __launch_bounds__(LOSS_THREADS) loss_grad_kernel(const __nv_bflo
                                                                  const float* __restrict__ coef,  // [N][2][C]
                                                                  const float* __restrict__ kce,   // [1]
                                                                  __nv_bfloat16* __restrict__ dlogits, int C,
-                                                                 long long S) {
+                                                                 long long S, uint32_t* __restrict__ status) {
   const int n = blockIdx.y;
   float alpha[CP], beta[CP];
 #pragma unroll
@@ -173,9 +182,12 @@ __global__ void __launch_bounds__(LOSS_THREADS) loss_grad_kernel(const __nv_bflo
     float f[CP];
     const long long off = ((long long)n * S + v) * CP;
     load_logits<CP>(logits + off, f);
-    const int y = (int)load_label(labels, label_kind, (long long)n * S + v);
+    const long long y_raw = load_label(labels, label_kind, (long long)n * S + v);
+    const bool y_ok = y_raw >= 0 && y_raw < C;
+    const int y = y_ok ? (int)y_raw : -1;
+    if (!y_ok) report(status, ST_BAD_ARG, 62, (uint32_t)y_raw, (uint32_t)n);
     softmax_regs<CP>(f, C);
-    const float wy = (cw ? cw[y] : 1.f) * k_ce;
+    const float wy = y_ok ? (cw ? cw[y] : 1.f) * k_ce : 0.f;
     float dot = 0.f;
 #pragma unroll
     for (int c = 0; c < CP; ++c) {
@@ -211,18 +223,22 @@ extern "C" int sb_loss_blocks(long long S) {
 }
 
 // sums: [N][3C+2] floats; ws: [N][blocks][3C+2]
+// largest class count of the fused kernels (callers route wider heads to the framework formula)
+extern "C" int sb_loss_max_classes(void) { return LOSS_MAXC; }
+
 extern "C" int sb_loss_sums(const void* logits, const void* labels, int label_kind, const float* cw, float* ws,
-                            float* sums, int N, long long S, int C, int CP, int argmax_mode, cudaStream_t stream) {
+                            float* sums, int N, long long S, int C, int CP, int argmax_mode, uint32_t* status,
+                            cudaStream_t stream) {
   if (C > CP || CP % 8 != 0 || CP > LOSS_MAXC) return SB_ERR_SHAPE;
   if (label_kind != 2 && label_kind != 4 && label_kind != 8) return SB_ERR_SHAPE;
   const int blocks = sb_loss_blocks(S);
   dim3 grid(blocks, N);
   const __nv_bfloat16* lg = (const __nv_bfloat16*)logits;
   switch (CP) {
-    case 8: loss_sums_kernel<8><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode); sb_count_launch(1); break;
-    case 16: loss_sums_kernel<16><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode); sb_count_launch(1); break;
-    case 24: loss_sums_kernel<24><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode); sb_count_launch(1); break;
-    case 32: loss_sums_kernel<32><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode); sb_count_launch(1); break;
+    case 8: loss_sums_kernel<8><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode, status); sb_count_launch(1); break;
+    case 16: loss_sums_kernel<16><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode, status); sb_count_launch(1); break;
+    case 24: loss_sums_kernel<24><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode, status); sb_count_launch(1); break;
+    case 32: loss_sums_kernel<32><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, ws, C, S, argmax_mode, status); sb_count_launch(1); break;
     default: return SB_ERR_SHAPE;
   }
   loss_finalize_kernel<<<N, 128, 0, stream>>>(ws, sums, blocks, 3 * C + 2);
@@ -232,17 +248,17 @@ extern "C" int sb_loss_sums(const void* logits, const void* labels, int label_ki
 
 extern "C" int sb_loss_grad(const void* logits, const void* labels, int label_kind, const float* cw,
                             const float* coef, const float* kce, void* dlogits, int N, long long S, int C, int CP,
-                            cudaStream_t stream) {
+                            uint32_t* status, cudaStream_t stream) {
   if (C > CP || CP % 8 != 0 || CP > LOSS_MAXC) return SB_ERR_SHAPE;
   const int blocks = sb_loss_blocks(S) * 2;
   dim3 grid(blocks, N);
   const __nv_bfloat16* lg = (const __nv_bfloat16*)logits;
   __nv_bfloat16* dl = (__nv_bfloat16*)dlogits;
   switch (CP) {
-    case 8: loss_grad_kernel<8><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S); sb_count_launch(1); break;
-    case 16: loss_grad_kernel<16><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S); sb_count_launch(1); break;
-    case 24: loss_grad_kernel<24><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S); sb_count_launch(1); break;
-    case 32: loss_grad_kernel<32><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S); sb_count_launch(1); break;
+    case 8: loss_grad_kernel<8><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S, status); sb_count_launch(1); break;
+    case 16: loss_grad_kernel<16><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S, status); sb_count_launch(1); break;
+    case 24: loss_grad_kernel<24><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S, status); sb_count_launch(1); break;
+    case 32: loss_grad_kernel<32><<<grid, LOSS_THREADS, 0, stream>>>(lg, labels, label_kind, cw, coef, kce, dl, C, S, status); sb_count_launch(1); break;
     default: return SB_ERR_SHAPE;
   }
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;

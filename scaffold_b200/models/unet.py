@@ -87,7 +87,8 @@ class Up(nn.Module):
             x1 = F.pad(x1, [dx // 2, dx - dx // 2, dy // 2, dy - dy // 2, dz // 2, dz - dz // 2])
         if use_cuda_kernels(x2):
             return self.conv([x2, x1])  # read as two channel segments, never concatenated
-        dtype = torch.get_autocast_dtype(x2.device.type) if torch.is_autocast_enabled(x2.device.type) else x2.dtype
+        dev = x2.device.type
+        dtype = torch.get_autocast_dtype(dev) if dev in ("cpu", "cuda") and torch.is_autocast_enabled(dev) else x2.dtype
         return self.conv(torch.cat([x2.to(dtype), x1.to(dtype)], dim=1))
 
 

@@ -202,7 +202,15 @@ SITES = {
     33: "plane wgrad: epilogue waiting for the accumulators",
     41: "gradient all-reduce: waiting for the peers' gradients",
     42: "gradient all-reduce: waiting for the peers' completion",
+    61: "fused loss: a label outside [0, n_classes) (detail = label value, sample); the voxel was skipped",
+    62: "fused loss gradient: a label outside [0, n_classes) (detail = label value, sample); the voxel was skipped",
 }
+
+CODES = {1: "mbarrier wait ran out", 2: "flag wait ran out", 3: "bad argument seen on the device"}
+
+
+class DeviceArgumentError(RuntimeError):
+    """A kernel met data it refuses to use (e.g. a label outside the class range) and skipped it."""
 
 
 class DeviceWaitTimeout(RuntimeError):
@@ -224,6 +232,10 @@ def check_status(device=None) -> None:
         if device is not None and (torch.device(device).index or 0) != key:
             continue
         v = t.cpu().tolist()
+        if v[0] == 3:
+            t.zero_()
+            raise DeviceArgumentError(
+                f"{SITES.get(v[1], 'site %d' % v[1])}: detail {v[2] if v[2] < 2 ** 31 else v[2] - 2 ** 32}, {v[3]}")
         if v[0] != 0:
             t.zero_()
             raise DeviceWaitTimeout(

@@ -15,6 +15,17 @@ import torch
 from . import _lib
 
 _lib.register("sb_gn_nsplit", [C.c_int, C.c_longlong, C.c_int], C.c_int)
+_lib.register("sb_gn_supported", [C.c_int, C.c_int], C.c_int)
+
+
+def supported(channels: int, groups: int) -> bool:
+    """Host-side statement of what the kernels cover (same rule as ``gn_channels_ok`` in ``csrc/group_norm.cu``)."""
+    if channels < 8 or channels % 8 or channels > 2048 or groups < 1 or groups > 256 or channels % groups:
+        return False
+    cg = channels // groups
+    if (8 % cg) if cg < 8 else (cg % 8):
+        return False
+    return not (cg < 8 and 8 // cg > 4)
 
 
 class SbGnArgs(C.Structure):

@@ -10,6 +10,7 @@ format, and the ReLU is applied on every path (ScaFFold/unet/group_norm.py:662-6
 """
 from __future__ import annotations
 
+import logging
 from typing import Optional
 
 import torch
@@ -54,6 +55,7 @@ class GroupNorm(nn.GroupNorm):
             raise ValueError(f"activation must be None or 'relu'; got {activation!r}")
         self.activation = activation
         self._spatial = None  # parallel.spatial.SpatialContext, set by the model wrapper
+        self._warned = False
 
     def set_spatial(self, ctx) -> None:
         self._spatial = ctx
@@ -61,11 +63,21 @@ class GroupNorm(nn.GroupNorm):
     def extra_repr(self) -> str:
         return super().extra_repr() + f", activation={self.activation}"
 
+    def kernel_supported(self) -> bool:
+        """True when ``csrc/group_norm.cu`` covers this (channels, groups) pair: C a multiple of 8 up to 2048 and a
+        group that is a whole number of channel octets (or 2 / 4 channels). Other pairs run the ATen formula."""
+        return self.affine and gk.supported(self.num_channels, self.num_groups)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         relu = self.activation == "relu"
-        if use_cuda_kernels(x) and self.affine and x.dim() == 5 and self.num_channels % 8 == 0:
+        if use_cuda_kernels(x) and x.dim() == 5 and self.kernel_supported():
             y = _GnFn.apply(to_vm(x), self.weight, self.bias, self.num_groups, self.eps, relu, self._spatial)
             return from_vm(y)
+        if x.is_cuda and use_cuda_kernels(x) and not self._warned:
+            self._warned = True
+            logging.getLogger("scaffold").warning(
+                "GroupNorm(%d groups, %d channels) is outside the sm_100a kernels' range; this layer runs ATen",
+                self.num_groups, self.num_channels)
         if self._spatial is not None and self._spatial.size > 1 and self._spatial.gn_global:
             y = self._spatial.group_norm_reference(x, self.num_groups, self.weight, self.bias, self.eps)
         else:

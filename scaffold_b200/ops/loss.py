@@ -28,8 +28,14 @@ from . import _lib
 
 _P = C.c_void_p
 _lib.register("sb_loss_blocks", [C.c_longlong], C.c_int)
-_lib.register("sb_loss_sums", [_P, _P, C.c_int, _P, _P, _P, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_int, _P])
-_lib.register("sb_loss_grad", [_P, _P, C.c_int, _P, _P, _P, _P, C.c_int, C.c_longlong, C.c_int, C.c_int, _P])
+_lib.register("sb_loss_sums", [_P, _P, C.c_int, _P, _P, _P, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_int, _P, _P])
+_lib.register("sb_loss_grad", [_P, _P, C.c_int, _P, _P, _P, _P, C.c_int, C.c_longlong, C.c_int, C.c_int, _P, _P])
+
+FUSED_MAX_CLASSES = 32  # widest head of csrc/loss.cu (LOSS_MAXC); wider heads take the PyTorch formula
+
+
+def fused_supported(n_classes: int) -> bool:
+    return 1 <= n_classes <= FUSED_MAX_CLASSES
 
 EPS = 1e-6
 
@@ -113,7 +119,7 @@ def _sums(logits_vm: torch.Tensor, labels: torch.Tensor, n_classes: int, cw, arg
     labels = labels.contiguous()
     _lib.check(L.sb_loss_sums(logits_vm.data_ptr(), labels.data_ptr(), _LABEL_KIND[labels.dtype], _lib.ptr(cw),
                               ws.data_ptr(), sums.data_ptr(), n, s, n_classes, cp, 1 if argmax else 0,
-                              _lib.stream_ptr()), "sb_loss_sums")
+                              _lib.status_tensor(logits_vm.device).data_ptr(), _lib.stream_ptr()), "sb_loss_sums")
     return sums
 
 
@@ -158,7 +164,8 @@ class _FusedLossFn(torch.autograd.Function):
         lab = lab.contiguous()
         _lib.check(_lib.lib().sb_loss_grad(logits_vm.data_ptr(), lab.data_ptr(), _LABEL_KIND[lab.dtype],
                                            _lib.ptr(ctx.cw), coef.data_ptr(), kce.data_ptr(), dl.data_ptr(), n,
-                                           d * h * w, ctx.c, cp, _lib.stream_ptr()), "sb_loss_grad")
+                                           d * h * w, ctx.c, cp, _lib.status_tensor(logits_vm.device).data_ptr(),
+                                           _lib.stream_ptr()), "sb_loss_grad")
         return dl, None, None, None, None
 
 

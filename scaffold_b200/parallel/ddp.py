@@ -7,9 +7,11 @@ gradient buffer over all ranks; the optimizer then applies ``1 / ddp_ranks``
 produces in the reference (ScaFFold/worker.py:81-97, ScaFFold/unet/conv3d.py:66-71).
 
 Backends: ``"fused"`` reduces through peer memory with the kernel of
-``csrc/peer.cu`` when it is available for the launch, ``"nccl"`` (and
-every CPU/gloo run) calls ``torch.distributed.all_reduce`` on buckets of the
-flat buffer.
+``csrc/peer.cu``; ``"nccl"`` (and every CPU/gloo run) calls
+``torch.distributed.all_reduce`` on buckets of the flat buffer. A ``"fused"``
+request that cannot be served (peer mapping refused, more than 8 ranks) is an
+error unless ``allow_fallback`` is set, in which case the reducer logs the reason
+and uses NCCL; ``effective_backend`` says which of the two runs.
 
 Overlap: on CUDA the flat buffer is cut into buckets in the order backward
 fills it (last layer first). A post-accumulate hook per parameter counts a
@@ -30,7 +32,7 @@ import torch.distributed as dist
 
 class GradReducer:
     def __init__(self, layout, flat=None, params=None, backend: str = "nccl", bucket_mb: int = 256,
-                 overlap: bool = False, overlap_bucket_mb: int = 32):
+                 overlap: bool = False, overlap_bucket_mb: int = 32, allow_fallback: bool = False):
         self.layout = layout
         self.flat = flat
         self.params = list(params) if params is not None else None
@@ -38,12 +40,16 @@ class GradReducer:
         self.bucket_elems = bucket_mb * (1 << 20) // 4
         self.world = layout.world_size if layout is not None else 1
         self._fused = None
-        if backend == "fused" and self.world > 1 and flat is not None:
+        if backend == "fused" and self.world > 1 and flat is not None and flat.grad.is_cuda:
             try:
                 from .fused_allreduce import FusedAllReduce
                 self._fused = FusedAllReduce(flat.numel)
                 flat.rehome_grad(self._fused.grad)  # gradients now accumulate straight into peer-visible memory
-            except Exception as exc:  # documented degradation: the NCCL path is always correct
+            except Exception as exc:
+                if not allow_fallback:
+                    raise RuntimeError(
+                        f"grad_allreduce='fused' was requested but the peer-memory reducer could not be set up "
+                        f"({type(exc).__name__}: {exc}); choose grad_allreduce='nccl' or set allow_fallback") from exc
                 import logging
                 logging.getLogger("scaffold").warning("fused gradient all-reduce unavailable (%s); using NCCL", exc)
                 self._fused = None
@@ -103,6 +109,15 @@ class GradReducer:
         torch.cuda.current_stream().wait_stream(self._comm)
         for b in self._buckets:
             b["pending"], b["launched"] = b["n"], False
+
+    @property
+    def effective_backend(self) -> str:
+        """'none' (one rank), 'fused' (peer-memory kernel) or 'nccl' / 'gloo' (library all-reduce)."""
+        if self.world == 1:
+            return "none"
+        if self._fused is not None:
+            return "fused"
+        return dist.get_backend() if dist.is_initialized() else "nccl"
 
     @property
     def scale(self) -> float:

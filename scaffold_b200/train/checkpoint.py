@@ -82,6 +82,7 @@ class CheckpointManager:
         self.log = log
         self.rank = D.get_world_rank()
         self.best_val_loss = float("inf")
+        self._best_before_pending = float("inf")  # value to return to when an asynchronous write fails
         self.async_save = bool(async_save)
         self._pool: Optional[ThreadPoolExecutor] = ThreadPoolExecutor(max_workers=1) if self.async_save else None
         self._pending: Optional[Future] = None
@@ -152,8 +153,6 @@ class CheckpointManager:
              extras: Optional[Dict[str, Any]] = None) -> bool:
         """Collective. Returns True when this checkpoint is the new best."""
         is_best = bool(val_loss_avg < self.best_val_loss)
-        if is_best:
-            self.best_val_loss = float(val_loss_avg)
         err = None
         if self.rank == 0:
             err = self._collect_pending()
@@ -176,13 +175,28 @@ class CheckpointManager:
                         self._write(payload, is_best)
                 except Exception as exc:
                     err = f"{type(exc).__name__}: {exc}"
-        self._agree(err)
+        self._agree_or_roll_back(err)
+        # only a save that every rank knows succeeded (or, asynchronous, was handed to the writer) moves the mark;
+        # the previous value is kept until the writer's outcome is collected
+        confirmed = self.best_val_loss
+        if is_best:
+            self.best_val_loss = float(val_loss_avg)
+        self._best_before_pending = confirmed if self._pool is not None else self.best_val_loss
         return is_best
+
+    def _agree_or_roll_back(self, err: Optional[str]) -> None:
+        """Agree on ``err``; a failure also takes back a 'best' mark set for a write that never landed."""
+        try:
+            self._agree(err)
+        except CheckpointSaveError:
+            self.best_val_loss = self._best_before_pending
+            raise
 
     def finalize_saves(self) -> None:
         """Collective: wait for the asynchronous writer and agree on its outcome."""
         err = self._collect_pending() if self.rank == 0 else None
-        self._agree(err)
+        self._agree_or_roll_back(err)
+        self._best_before_pending = self.best_val_loss
 
     def close(self) -> None:
         if self._pool is not None:

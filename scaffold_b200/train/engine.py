@@ -24,7 +24,7 @@ from ..utils.perf import region
 class TrainEngine:
     def __init__(self, model, optimizer, n_classes: int, device, layout=None, spatial=None,
                  class_weights: Optional[torch.Tensor] = None, amp: bool = True, grad_backend: str = "nccl",
-                 max_norm: float = 1.0, grad_overlap: bool = False):
+                 max_norm: float = 1.0, grad_overlap: bool = False, allow_fallback: bool = False):
         self.model, self.optimizer = model, optimizer
         self.n_classes = n_classes
         self.device = torch.device(device)
@@ -33,9 +33,12 @@ class TrainEngine:
         self.amp = amp
         self.max_norm = max_norm
         self.cuda = self.device.type == "cuda"
+        # the fused loss kernels keep one voxel's classes in registers (at most 32); wider heads use the PyTorch formula
+        self.fused_loss = self.cuda and self.amp and L.fused_supported(n_classes)
         self.flat = optimizer.attach() if isinstance(optimizer, FusedClipAdam) else None
         params = [p for p in model.parameters() if p.requires_grad]
-        self.reducer = GradReducer(layout, flat=self.flat, params=params, backend=grad_backend, overlap=grad_overlap)
+        self.reducer = GradReducer(layout, flat=self.flat, params=params, backend=grad_backend, overlap=grad_overlap,
+                                   allow_fallback=allow_fallback)
         if isinstance(optimizer, FusedClipAdam):
             optimizer.reduce_scale = self.reducer.scale
         self.last_ce = self.last_dice = None
@@ -62,7 +65,7 @@ class TrainEngine:
     def forward_loss(self, images: torch.Tensor, masks: torch.Tensor):
         """Returns (loss, ce, foreground soft dice, logits-or-None)."""
         with region("predict"):
-            fused = self.cuda and self.amp
+            fused = self.fused_loss
             with self._autocast():
                 if fused:
                     logits_vm = self.model.forward_padded_logits(images)
@@ -124,7 +127,7 @@ class TrainEngine:
         """Returns (loss, hard-dice per (sample, class)) for one validation batch."""
         images, masks = self.to_device(images, masks)
         loss, ce, fg, logits = self.forward_loss(images, masks)
-        if self.cuda and self.amp:
+        if self.fused_loss:
             dice = L.hard_dice_fused(logits, masks, self.n_classes, self.spatial)
         else:
             dice = L.hard_dice_reference(logits.float(), masks, self.n_classes, self.spatial)

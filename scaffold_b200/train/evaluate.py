@@ -8,6 +8,8 @@ this rank; the caller reduces over the data-parallel replicas.
 """
 from __future__ import annotations
 
+import sys
+
 import torch
 
 
@@ -21,12 +23,9 @@ def evaluate(engine, dataloader, progress: bool = False):
     loss_sum = torch.zeros((), device=device)
     n_batches = n_samples = 0
     it = dataloader
-    if progress:
-        try:
-            from tqdm import tqdm
-            it = tqdm(dataloader, desc="Validation round", unit="batch", leave=False, disable=True)
-        except Exception:
-            it = dataloader
+    if progress and sys.stderr.isatty():  # a progress bar only where someone watches; logs stay clean
+        from tqdm import tqdm
+        it = tqdm(dataloader, desc="validation", unit="batch", leave=False)
     for batch in it:
         bs = batch["image"].shape[0]
         loss, dice = engine.eval_step(batch["image"], batch["mask"])
@@ -37,4 +36,7 @@ def evaluate(engine, dataloader, progress: bool = False):
     if was_training:
         model.train()
     d, l = float(dice_sum.item()), float(loss_sum.item())  # the one host sync
+    if device.type == "cuda":
+        from ..ops import _lib
+        _lib.check_status(device)  # a bounded device wait that ran out, or a label the loss kernel refused
     return d, l, (l / n_samples if n_samples else 0.0), n_batches, n_samples

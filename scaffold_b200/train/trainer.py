@@ -57,39 +57,46 @@ class UnpaddedDistributedSampler(Sampler):
         return None
 
 
-def sample_ce_weight_indices(n_train: int, fraction: float) -> List[int]:
-    count = max(1, min(n_train, int(math.ceil(n_train * float(fraction)))))
-    step = n_train / count
-    return sorted({min(n_train - 1, int(i * step)) for i in range(count)})
+def sample_ce_weight_indices(n_train: int, fraction: Optional[float]) -> List[int]:
+    """Evenly spaced mask indices, first and last included (the float32 ``linspace`` rule of
+    ScaFFold/utils/losses.py:24-39, so both implementations weigh the same masks); all of them when the
+    fraction rounds up to the whole split."""
+    if n_train <= 0:
+        return []
+    count = max(1, math.ceil(n_train * float(0.1 if fraction is None else fraction)))
+    if count >= n_train:
+        return list(range(n_train))
+    return torch.linspace(0, n_train - 1, steps=count).long().tolist()
 
 
 def compute_ce_class_weights(train_set, n_categories: int, device, sample_fraction: float = 0.1, log=None):
-    """Background vs foreground inverse-frequency weights from a sample of training masks, summed over ranks."""
-    num_classes = n_categories + 1
-    weights = torch.ones(num_classes, device=device, dtype=torch.float32)
-    n_train = len(train_set)
-    if n_train == 0:
-        if log is not None:
-            log.warning("Training set is empty while computing CE class weights. Falling back to uniform weights.")
-        return weights
-    idx = sample_ce_weight_indices(n_train, sample_fraction)
-    counts = torch.zeros(num_classes, dtype=torch.long)
-    for i in idx:
-        mask = train_set.load_mask_only(i) if hasattr(train_set, "load_mask_only") else train_set[i]["mask"]
-        counts += torch.bincount(mask.reshape(-1).long(), minlength=num_classes)[:num_classes]
-    counts = counts.to(device)
+    """Cross-entropy class weights ``total / background`` for class 0 and ``total / foreground`` shared by all
+    fractal classes, from the voxel histogram of a sample of training masks (local shards, summed over ranks).
+    Uniform weights when the sample lacks either kind of voxel. Role of ScaFFold/utils/losses.py:42-114."""
+    n_cls = n_categories + 1
+    picked = sample_ce_weight_indices(len(train_set), sample_fraction)
+    mask_of = getattr(train_set, "load_mask_only", None) or (lambda i: train_set[i]["mask"])
+    hist = torch.zeros(n_cls, dtype=torch.long)
+    for i in picked:
+        hist += torch.bincount(mask_of(i).reshape(-1).long(), minlength=n_cls)[:n_cls]
+    hist = hist.to(device)
     if dist.is_initialized() and dist.get_world_size() > 1:
-        dist.all_reduce(counts)
-    bg, fg = int(counts[0].item()), int(counts[1:].sum().item())
-    if bg > 0 and fg > 0:
-        weights[0] = (bg + fg) / bg
-        weights[1:] = (bg + fg) / fg
-    elif log is not None:
-        log.warning("Sampled masks did not contain both background and foreground voxels. Falling back to uniform "
-                    "CE weights.")
+        dist.all_reduce(hist)  # every rank sampled its own shard of the same masks
+    bg, fg = (int(v) for v in (hist[0], hist[1:].sum()))
+    weights = torch.ones(n_cls, device=device, dtype=torch.float32)
+    usable = bg > 0 and fg > 0
+    if usable:
+        weights[0], weights[1:] = (bg + fg) / bg, (bg + fg) / fg
     if log is not None:
-        log.info("CE weights estimated from %d training masks (sample_fraction=%s): background_voxels=%d "
-                 "foreground_voxels=%d weights=%s", len(idx), sample_fraction, bg, fg, weights.cpu().tolist())
+        if not picked:
+            log.warning("class weights: the training split is empty; every class weighs 1")
+        elif not usable:
+            log.warning("class weights: %d sampled masks hold %d background and %d foreground voxels; one kind is "
+                        "missing, so every class weighs 1", len(picked), bg, fg)
+        else:
+            log.info("class weights from masks %s (fraction %s): %d background / %d foreground voxels -> "
+                     "background %.4f, foreground %.4f", picked, sample_fraction, bg, fg, float(weights[0]),
+                     float(weights[-1]))
     return weights
 
 
@@ -161,7 +168,33 @@ class Trainer:
         self.engine = TrainEngine(self.model, self.optimizer, self.n_classes, self.device, layout=self.layout,
                                   spatial=self.spatial, class_weights=self.ce_class_weights,
                                   amp=bool(cfg.torch_amp), grad_backend=getattr(cfg, "grad_allreduce", "nccl"),
-                                  grad_overlap=bool(getattr(cfg, "grad_overlap", False)))
+                                  grad_overlap=bool(getattr(cfg, "grad_overlap", False)),
+                                  allow_fallback=bool(getattr(cfg, "allow_fallback", False)))
+        self._log_kernel_selection()
+
+    def _log_kernel_selection(self) -> None:
+        """Once per run, rank 0: the kernel every layer routes to and which peer-memory channels are live
+        (role of the start-up report of ScaFFold/utils/trainer.py:808-830)."""
+        if self.world_rank != 0:
+            return
+        from ..ops.selection import effective_backends, format_selection, kernel_selection
+        channels = effective_backends(self.engine)
+        if self.device.type != "cuda" or not self.engine.amp:
+            self.log.info("kernel selection: %s run without bf16 autocast -> every layer runs ATen; channels: %s",
+                          self.device.type, channels)
+            return
+        cfg = self.config
+        shards = self.layout.num_shards if self.layout is not None else (1, 1, 1)
+        dims = self.layout.shard_dim if self.layout is not None else (2, 3, 4)
+        local = [int(cfg.vol_size)] * 3
+        for n, d in zip(shards, dims):
+            local[d - 2] = -(-local[d - 2] // n)
+        try:
+            rows = kernel_selection(self.model, int(cfg.local_batch_size), local, self.spatial)
+            self.log.info("kernel selection (local volume %s, batch %s):\n%s", "x".join(map(str, local)),
+                          cfg.local_batch_size, format_selection(rows, channels))
+        except Exception as exc:  # the report must never stop a run
+            self.log.warning("kernel selection report failed: %s", exc)
 
     # -- reductions -----------------------------------------------------------------
     def _all_reduce_data_parallel(self, t: torch.Tensor) -> None:
@@ -267,8 +300,8 @@ class Trainer:
         try:
             while val_score < cfg.target_dice:
                 if cfg.epochs != -1 and epoch > cfg.epochs:
-                    self.log.warning("Maximum epochs reached '%s'. Concluding training early (may have not converged).",
-                                     cfg.epochs)
+                    self.log.warning("stopping after the configured %s epochs with validation Dice %.4f below the "
+                                     "target %s", cfg.epochs, val_score, cfg.target_dice)
                     break
                 t0 = time.time()
                 self.train_sampler.set_epoch(epoch)

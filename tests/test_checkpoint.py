@@ -101,3 +101,48 @@ def test_snapshot_restore_puts_everything_back():
     for a, b in zip(before, model.parameters()):
         assert torch.equal(a, b)
     assert torch.equal(torch.rand(1), r0) and sched.last_epoch == 0
+
+
+def test_failed_write_does_not_move_the_best_mark(tmp_path, monkeypatch):
+    model, opt, sched = _bits()
+    mgr = ck.CheckpointManager(tmp_path, "checkpoints")
+    assert mgr.save(1, 0.8, model, opt, sched) is True
+    real_save = ck.torch.save
+
+    def failing(obj, f, *a, **k):
+        raise OSError("quota exceeded")
+
+    monkeypatch.setattr(ck.torch, "save", failing)
+    with pytest.raises(ck.CheckpointSaveError):
+        mgr.save(2, 0.3, model, opt, sched)  # would have been the new best
+    assert mgr.best_val_loss == 0.8
+    monkeypatch.setattr(ck.torch, "save", real_save)
+    assert mgr.save(3, 0.5, model, opt, sched) is True  # 0.5 beats the 0.8 that is really on disk
+    assert torch.load(mgr.best_path, weights_only=False)["epoch"] == 3
+
+
+def test_failed_async_write_rolls_the_best_mark_back(tmp_path, monkeypatch):
+    model, opt, sched = _bits()
+    mgr = ck.CheckpointManager(tmp_path, "checkpoints", async_save=True)
+    assert mgr.save(1, 0.8, model, opt, sched) is True
+    mgr.finalize_saves()
+
+    def failing(obj, f, *a, **k):
+        raise OSError("writer died")
+
+    monkeypatch.setattr(ck.torch, "save", failing)
+    assert mgr.save(2, 0.3, model, opt, sched) is True  # handed to the writer; the failure surfaces later
+    with pytest.raises(ck.CheckpointSaveError, match="writer died"):
+        mgr.finalize_saves()
+    assert mgr.best_val_loss == 0.8
+    mgr.close()
+
+
+def test_ce_weight_indices_follow_the_linspace_rule():
+    from scaffold_b200.train.trainer import sample_ce_weight_indices as pick
+    assert pick(100, 0.1) == [0, 11, 22, 33, 44, 55, 66, 77, 88, 99]
+    assert pick(10, 1.0) == list(range(10))
+    assert pick(10, 0.95) == list(range(10))  # the fraction rounds up to the whole split
+    assert pick(7, 0.01) == [0]
+    assert pick(0, 0.1) == []
+    assert pick(50, None) == [0, 12, 24, 36, 49]
