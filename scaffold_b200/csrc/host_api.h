@@ -72,6 +72,12 @@ typedef struct {
   void* dgrad_kd;
 } SbPackArgs;
 
+// One entry of the whole-model packing table (sb_pack_conv3_batch): tile0 / tiles_x are filled by sb_pack_conv3_plan.
+typedef struct {
+  SbPackArgs a;
+  int tile0, tiles_x;
+} SbPackJob;
+
 // k=2,s=2 transposed convolution. Forward: src [N,D,H,W,cin] -> dst
 // [N,2D,2H,2W,cout], wpack bf16 [8*cout][cin] (row = tap*cout + co).
 // Backward-data (sb_convT_dgrad): src = gy [N,2D,2H,2W,cout] -> dst = gx

@@ -10,7 +10,8 @@
 // zeroed once by the caller and reused every step.
 //
 // Role of the reference: the weight re-layout that triton_conv3d's adapters do with torch ops before
-// each launch (triton_conv3d/gather_gemm.py:344-420); here it is one kernel per layer and step.
+// each launch (triton_conv3d/gather_gemm.py:344-420); here it is one kernel per layer (first use) or one
+// kernel for the whole model (sb_pack_conv3_batch, launched by the optimizer right after the update).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -31,13 +32,13 @@ __device__ __forceinline__ int kd_pos(int p) {  // (kd,kh,kw) index -> (kh,kw,2-
 constexpr int PK_LD = PK_T + 2;
 constexpr int PK_PLANE = PK_T * PK_LD + 2;  // one tap's plane; the odd word count spreads taps over banks
 
-__global__ void __launch_bounds__(256) pack_conv3_kernel(SbPackArgs a) {
-  extern __shared__ __nv_bfloat16 tile[];  // [27] planes of [PK_T][PK_LD]
+// One 32 x 32 (output x input channel) tile of one layer; `tile` is the CTA's dynamic shared memory.
+__device__ __forceinline__ void pack_tile(const SbPackArgs& a, const int bx, const int by, __nv_bfloat16* tile) {
   __nv_bfloat16* const o_fwd = (__nv_bfloat16*)a.fwd;
   __nv_bfloat16* const o_fwd_kd = (__nv_bfloat16*)a.fwd_kd;
   __nv_bfloat16* const o_dgrad = (__nv_bfloat16*)a.dgrad;
   __nv_bfloat16* const o_dgrad_kd = (__nv_bfloat16*)a.dgrad_kd;
-  const int co0 = blockIdx.x * PK_T, ci0 = blockIdx.y * PK_T;
+  const int co0 = bx * PK_T, ci0 = by * PK_T;
   const int nco = min(PK_T, a.cout - co0), nci = min(PK_T, a.cin - ci0);
   const int run = nci * 27;
   if (nci == PK_T && (a.cin % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.w) & 15) == 0)) {
@@ -146,18 +147,73 @@ __global__ void __launch_bounds__(256) pack_conv3_kernel(SbPackArgs a) {
   }
 }
 
+__global__ void __launch_bounds__(256) pack_conv3_kernel(SbPackArgs a) {
+  extern __shared__ __nv_bfloat16 tile[];  // [27] planes of [PK_T][PK_LD]
+  pack_tile(a, blockIdx.x, blockIdx.y, tile);
+}
+
+// All layers of a model in one launch: block b belongs to the job with tile0 <= b < tile0 + tiles.
+__global__ void __launch_bounds__(256) pack_conv3_batch_kernel(const SbPackJob* __restrict__ jobs, int njobs) {
+  extern __shared__ __nv_bfloat16 tile[];
+  __shared__ int job_s;
+  if (threadIdx.x == 0) {
+    int j = 0;
+    while (j + 1 < njobs && (int)blockIdx.x >= jobs[j + 1].tile0) ++j;
+    job_s = j;
+  }
+  __syncthreads();
+  const SbPackJob& jb = jobs[job_s];
+  const int t = blockIdx.x - jb.tile0;
+  pack_tile(jb.a, t % jb.tiles_x, t / jb.tiles_x, tile);
+}
+
 }  // namespace sb
 
-extern "C" int sb_pack_conv3(const SbPackArgs* a, cudaStream_t stream) {
+static int pack_configure(int smem) {
   static bool configured = false;
-  const int smem = 27 * sb::PK_PLANE * (int)sizeof(__nv_bfloat16);
   if (!configured) {
-    if (cudaFuncSetAttribute(sb::pack_conv3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(sb::pack_conv3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(sb::pack_conv3_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return SB_ERR_DRIVER;
     configured = true;
   }
-  if (a->cout <= 0 || a->cin <= 0 || a->real0 > a->pad0 || a->cin - a->real0 + a->pad0 > a->cin_pad || a->cout > a->cout_pad)
-    return SB_ERR_SHAPE;
+  return 0;
+}
+
+static bool pack_args_ok(const SbPackArgs* a) {
+  return !(a->cout <= 0 || a->cin <= 0 || a->real0 > a->pad0 || a->cin - a->real0 + a->pad0 > a->cin_pad ||
+           a->cout > a->cout_pad);
+}
+
+// Fills tile0 / tiles_x of `njobs` host-side jobs (validating each) and returns the total tile count, or -1.
+extern "C" long long sb_pack_conv3_plan(SbPackJob* jobs, int njobs) {
+  long long total = 0;
+  for (int j = 0; j < njobs; ++j) {
+    if (!pack_args_ok(&jobs[j].a)) return -1;
+    jobs[j].tile0 = (int)total;
+    jobs[j].tiles_x = (jobs[j].a.cout + sb::PK_T - 1) / sb::PK_T;
+    total += (long long)jobs[j].tiles_x * ((jobs[j].a.cin + sb::PK_T - 1) / sb::PK_T);
+    if (total > 0x7fffffffLL) return -1;
+  }
+  return total;
+}
+
+// dev_jobs: the planned job table copied to device memory by the caller (it stays valid while buffers persist).
+extern "C" int sb_pack_conv3_batch(const SbPackJob* dev_jobs, int njobs, long long total_tiles, cudaStream_t stream) {
+  const int smem = 27 * sb::PK_PLANE * (int)sizeof(__nv_bfloat16);
+  int rc = pack_configure(smem);
+  if (rc) return rc;
+  if (njobs < 1 || total_tiles < 1 || dev_jobs == nullptr) return SB_ERR_SHAPE;
+  sb::pack_conv3_batch_kernel<<<(unsigned)total_tiles, 256, smem, stream>>>(dev_jobs, njobs);
+  sb_count_launch(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
+extern "C" int sb_pack_conv3(const SbPackArgs* a, cudaStream_t stream) {
+  const int smem = 27 * sb::PK_PLANE * (int)sizeof(__nv_bfloat16);
+  int rc = pack_configure(smem);
+  if (rc) return rc;
+  if (!pack_args_ok(a)) return SB_ERR_SHAPE;
   dim3 grid((a->cout + sb::PK_T - 1) / sb::PK_T, (a->cin + sb::PK_T - 1) / sb::PK_T);
   sb::pack_conv3_kernel<<<grid, 256, smem, stream>>>(*a);
   sb_count_launch(1);

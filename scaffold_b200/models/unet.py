@@ -117,6 +117,7 @@ class UNet(nn.Module):
         self.group_norm_groups = group_norm_groups
         self.base_width = base_width
         self.checkpointing = False
+        self._spatial = None  # parallel.spatial.SpatialContext of a sharded run (see set_spatial)
         factor = 2 if trilinear else 1
         g = group_norm_groups
 
@@ -143,8 +144,20 @@ class UNet(nn.Module):
             return torch.utils.checkpoint.checkpoint(block, *inputs, use_reentrant=False)
         return block(*inputs)
 
+    def set_spatial(self, ctx) -> None:
+        """A volume split along H or W is processed with that axis exchanged with depth ('kernel space'):
+        the input is transposed on the way in and the logits on the way out (views, no copies)."""
+        self._spatial = ctx
+
+    def _swap(self, t: torch.Tensor) -> torch.Tensor:
+        sp = self._spatial
+        return t if sp is None or sp.lead_swap is None else sp.to_kernel_space(t)
+
     def features(self, x: torch.Tensor) -> torch.Tensor:
-        """Everything up to (not including) the 1x1x1 head."""
+        """Everything up to (not including) the 1x1x1 head (in kernel space on a sharded run)."""
+        x = self._swap(x)
+        if x.is_cuda and not x.is_contiguous():
+            x = x.contiguous()  # the input staging kernel reads a dense NCDHW tensor
         skips = [self._run(self.down_list[0], x)]
         for i in range(1, self.layers + 1):
             skips.append(self._run(self.down_list[i], skips[-1]))
@@ -156,10 +169,11 @@ class UNet(nn.Module):
 
     @annotate("UNet.forward")
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self._run(self.up_list[-1], self.features(x))
+        return self._swap(self._run(self.up_list[-1], self.features(x)))
 
     def forward_padded_logits(self, x: torch.Tensor) -> torch.Tensor:
-        """CUDA path: voxel-major bf16 logits ``[N, D, H, W, pad16(n_classes)]`` for the fused loss."""
+        """CUDA path: voxel-major bf16 logits ``[N, D, H, W, pad16(n_classes)]`` for the fused loss, in kernel
+        space (the caller exchanges the labels' axes the same way, ``SpatialContext.to_kernel_space``)."""
         return self.up_list[-1].conv.forward_padded(self.features(x))
 
     def use_checkpointing(self) -> None:

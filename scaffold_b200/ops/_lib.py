@@ -67,6 +67,10 @@ class SbPackArgs(C.Structure):
     ]
 
 
+class SbPackJob(C.Structure):
+    _fields_ = [("a", SbPackArgs), ("tile0", C.c_int), ("tiles_x", C.c_int)]
+
+
 class SbConvTArgs(C.Structure):
     _fields_ = [
         ("src", C.c_void_p),
@@ -138,6 +142,8 @@ _SIGNATURES = {
     "sb_conv_fwd": ([C.POINTER(SbConvArgs), _P], C.c_int),
     "sb_conv_fwd_workspace": ([C.POINTER(SbConvArgs)], C.c_longlong),
     "sb_pack_conv3": ([C.POINTER(SbPackArgs), _P], C.c_int),
+    "sb_pack_conv3_plan": ([C.POINTER(SbPackJob), C.c_int], C.c_longlong),
+    "sb_pack_conv3_batch": ([_P, C.c_int, C.c_longlong, _P], C.c_int),
     "sb_stage_input": ([_P, C.c_int, C.c_int, C.c_int, C.c_longlong, _P, C.c_int, _P], C.c_int),
     "sb_colsum_blocks": ([], C.c_int),
     "sb_colsum": ([_P, C.c_longlong, C.c_int, _P, C.c_int, _P, _P], C.c_int),

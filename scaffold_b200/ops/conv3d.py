@@ -17,6 +17,8 @@ CUDA path (role of ``_skip_concat``, ScaFFold/unet/unet_parts.py:76-120, and of
 """
 from __future__ import annotations
 
+import ctypes as C
+import weakref
 from typing import List, Optional, Sequence, Union
 
 import torch
@@ -24,7 +26,53 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from . import conv_kernels as ck
-from .layout import from_vm, to_vm, use_cuda_kernels, weights_epoch
+from .layout import direct_grad_target, from_vm, notify_grad_written, to_vm, use_cuda_kernels, weights_epoch
+
+
+_PACK_REGISTRY: "weakref.WeakSet[_PackCache]" = weakref.WeakSet()
+_PACK_PLAN = {"key": None, "table": None, "n": 0, "tiles": 0, "members": []}
+
+
+def repack_all() -> int:
+    """Refresh every 3x3x3 operand copy that any layer has asked for so far, in ONE kernel launch.
+
+    The optimizer calls this right after it updated the weights, so the next forward pass finds all
+    packs fresh instead of launching one packing kernel per layer (role of the weight repack that
+    the update kernel owes the convolutions). Returns the number of layers covered; layers that have
+    not run yet, or whose weight is a non-contiguous view, keep packing lazily on first use.
+    """
+    from . import _lib
+    members = []
+    for cache in list(_PACK_REGISTRY):
+        w = cache._w_ref() if cache._w_ref is not None else None
+        if w is None or not w.is_cuda or not w.is_contiguous() or w.dtype != torch.float32:
+            continue
+        for sig in sorted({k[1] for k in cache._asked}):
+            names = sorted(nm for nm, s_ in cache._asked if s_ == sig)
+            bufs = {nm: cache._bufs.get((nm, sig, w.device)) for nm in names}
+            if any(b is None for b in bufs.values()):
+                continue
+            members.append((cache, w, sig, cache._real[sig], bufs))
+    if not members:
+        return 0
+    key = tuple((id(c), w.data_ptr(), sig, tuple((n, b.data_ptr()) for n, b in sorted(bufs.items())))
+                for c, w, sig, _, bufs in members)
+    plan = _PACK_PLAN
+    if plan["key"] != key:
+        jobs = (_lib.SbPackJob * len(members))()
+        for j, (_, w, sig, real_c, bufs) in enumerate(members):
+            ck.fill_pack_args(jobs[j].a, w, sig, real_c, bufs)
+        total = _lib.lib().sb_pack_conv3_plan(jobs, len(members))
+        if total < 1:
+            raise _lib.NativeError("sb_pack_conv3_plan refused the packing table")
+        host = torch.frombuffer(bytearray(bytes(jobs)), dtype=torch.uint8)
+        plan.update(key=key, table=host.to(members[0][1].device), n=len(members), tiles=int(total))
+    _lib.check(_lib.lib().sb_pack_conv3_batch(plan["table"].data_ptr(), plan["n"], plan["tiles"], _lib.stream_ptr()),
+               "sb_pack_conv3_batch")
+    for cache, w, sig, _, bufs in members:
+        cache._sync(w)
+        cache._fresh.update((nm, sig) for nm in bufs)
+    return len(members)
 
 
 class _PackCache:
@@ -32,6 +80,8 @@ class _PackCache:
 
     def __init__(self):
         self._key = None
+        self._w_ref = None    # the parameter these copies belong to (set on first use)
+        self._real = {}       # source signature -> real channels per source
         self._vals = {}
         self._asked = set()   # (layout name, source signature) ever requested: packed together
         self._fresh = set()   # of those, the ones that hold the current weights
@@ -55,6 +105,10 @@ class _PackCache:
         name = kind + ("_kd" if kd else "")
         if (name, sig) not in self._fresh:
             self._asked.add((name, sig))
+            self._real[sig] = list(real_c)
+            if self._w_ref is None and isinstance(w, torch.nn.Parameter):
+                self._w_ref = weakref.ref(w)
+                _PACK_REGISTRY.add(self)
             group = [k for k in self._asked if k[1] == sig]
             want = {}
             co_pad, k_pad = ck.pad_channels(w.shape[0]), sum(sig)
@@ -124,6 +178,7 @@ class _ConvSameFn(torch.autograd.Function):
         (y,) = ck.conv_same(list(fwd_xs if fwd_xs is not None else xs), wf, ks, [cout_pad], bias=bpad,
                             out_dims=out_dims, in_off=in_off)
         ctx.mod = mod
+        ctx.wparam = weight  # the caller's tensor itself: backward may add into its flat-buffer .grad
         ctx.in_off, ctx.in_dims = in_off, in_dims
         ctx.src_c, ctx.real_c = src_c, real_c
         ctx.has_bias = bias is not None
@@ -154,11 +209,17 @@ class _ConvSameFn(torch.autograd.Function):
                     gxs[i] = o
         gw = gb = None
         if ctx.needs_input_grad[0]:
-            gw = torch.empty(weight.shape, dtype=torch.float32, device=weight.device)  # contiguous whatever the parameter layout
-            if list(src_c) == list(real_c):
+            direct = direct_grad_target(ctx.wparam) if list(src_c) == list(real_c) else None
+            if direct is not None:
+                # the ordered split-K reduce adds straight into the parameter's slice of the flat gradient buffer
+                ck.conv_wgrad(gy, list(xs), ks, direct, accumulate=True, x_off=ctx.in_off)
+                notify_grad_written(ctx.wparam)
+            elif list(src_c) == list(real_c):
+                gw = torch.empty(weight.shape, dtype=torch.float32, device=weight.device)  # contiguous whatever the parameter layout
                 ck.conv_wgrad(gy, list(xs), ks, gw, x_off=ctx.in_off)
             else:
                 # channel-padded sources (the 3-channel stem): gradient over padded Cin, then slice
+                gw = None
                 gwp = torch.empty((weight.shape[0], sum(src_c), ks, ks, ks), dtype=torch.float32, device=gy.device)
                 ck.conv_wgrad(gy, list(xs), ks, gwp, x_off=ctx.in_off)
                 parts, o = [], 0
@@ -184,6 +245,7 @@ class _ConvHaloFn(torch.autograd.Function):
         (y,) = ck.conv_same(list(xs), wf, 3, [cout_pad], halo=landing)
         ctx.halo_saved = landing.clone()  # the arena slot is recycled; backward needs the planes again
         ctx.mod, ctx.chan, ctx.src_c = mod, chan, src_c
+        ctx.wparam = weight
         ctx.save_for_backward(weight, *xs)
         return y
 
@@ -210,8 +272,13 @@ class _ConvHaloFn(torch.autograd.Function):
                     gxs[i] = o
         gw = None
         if ctx.needs_input_grad[0]:
-            gw = torch.empty(weight.shape, dtype=torch.float32, device=weight.device)  # contiguous whatever the parameter layout
-            ck.conv_wgrad(gy, list(xs), 3, gw, x_halo=ctx.halo_saved)
+            direct = direct_grad_target(ctx.wparam)
+            if direct is not None:
+                ck.conv_wgrad(gy, list(xs), 3, direct, accumulate=True, x_halo=ctx.halo_saved)
+                notify_grad_written(ctx.wparam)
+            else:
+                gw = torch.empty(weight.shape, dtype=torch.float32, device=weight.device)  # contiguous whatever the parameter layout
+                ck.conv_wgrad(gy, list(xs), 3, gw, x_halo=ctx.halo_saved)
         return (gw, None, None, None, *gxs)
 
 
@@ -226,6 +293,11 @@ class Conv3d(nn.Conv3d):
 
     def set_spatial(self, ctx) -> None:
         self._spatial = ctx
+
+    def _w(self) -> torch.Tensor:
+        """The weight as the kernels' axes see it: tap axes exchanged like the volume's (``lead_swap``), a view."""
+        k = getattr(self._spatial, "lead_swap", None)
+        return self.weight if k is None else self.weight.transpose(2, k)
 
     def _real_in_channels(self, src_c: Sequence[int]) -> List[int]:
         """Real (unpadded) channel count of each source; only a single source may be padded."""
@@ -254,9 +326,9 @@ class Conv3d(nn.Conv3d):
         if sp is not None and sp.size > 1 and self.kernel_size[0] > 1:
             # sharded volume: neighbours' boundary planes replace the zero padding on the split dims
             xin = sp.halo_pad(xin, self.kernel_size[0] // 2)
-            return F.conv3d(xin, self.weight, self.bias, self.stride, sp.conv_padding(self.kernel_size[0]),
+            return F.conv3d(xin, self._w(), self.bias, self.stride, sp.conv_padding(self.kernel_size[0]),
                             self.dilation, self.groups)
-        return super().forward(xin)
+        return self._conv_forward(xin, self._w(), self.bias)
 
     def _cuda_forward(self, xs) -> torch.Tensor:
         """Voxel-major output of the kernel path; on a sharded volume the sources first receive their halo."""
@@ -268,7 +340,7 @@ class Conv3d(nn.Conv3d):
             real = self._real_in_channels([v.shape[4] for v in vms])
             if h >= 8 and w >= 16 and d >= 2 and self.bias is None and real == [v.shape[4] for v in vms] \
                     and self.out_channels % 16 == 0:
-                return _ConvHaloFn.apply(self.weight, self.bias, self, sp.halo_channel, *vms)
+                return _ConvHaloFn.apply(self._w(), self.bias, self, sp.halo_channel, *vms)
         if sp is not None and sp.size > 1 and self.kernel_size[0] > 1:
             halo = self.kernel_size[0] // 2
             xs = [sp.halo_pad(t, halo) for t in xs]
@@ -280,7 +352,7 @@ class Conv3d(nn.Conv3d):
             # few input channels (the stem): the forward pass reads a copy padded to 32 channels so that it runs
             # the kd-fused kernel; the weight gradient keeps the 16-channel copy
             fwd_vms = (to_vm(xs[0], pad16=True, pad_to=32),)
-        return _ConvSameFn.apply(self.weight, self.bias, self, off, fwd_vms, *vms)
+        return _ConvSameFn.apply(self._w(), self.bias, self, off, fwd_vms, *vms)
 
     def forward_padded(self, x) -> torch.Tensor:
         """CUDA path only: voxel-major output with the channel axis padded to a multiple of 16."""
@@ -298,6 +370,7 @@ class _ConvTFn(torch.autograd.Function):
             b32 = mod._cache_b.get(bias, "b", lambda b: b.contiguous())
         y = ck.convT_fwd(x, wf, cout, b32)
         ctx.mod = mod
+        ctx.wparam = weight
         ctx.has_bias = bias is not None
         ctx.save_for_backward(weight, x)
         return y
@@ -312,8 +385,13 @@ class _ConvTFn(torch.autograd.Function):
             wd = mod._cache.get(weight, "dgrad", ck.pack_weight_convT_dgrad)
             gx = ck.convT_dgrad(gy, wd, x.shape[4])
         if ctx.needs_input_grad[0]:
-            gw = torch.empty(weight.shape, dtype=torch.float32, device=weight.device)  # contiguous whatever the parameter layout
-            ck.conv_wgrad(gy, [x], 2, gw)
+            direct = direct_grad_target(ctx.wparam)
+            if direct is not None:
+                ck.conv_wgrad(gy, [x], 2, direct, accumulate=True)
+                notify_grad_written(ctx.wparam)
+            else:
+                gw = torch.empty(weight.shape, dtype=torch.float32, device=weight.device)  # contiguous whatever the parameter layout
+                ck.conv_wgrad(gy, [x], 2, gw)
         if ctx.has_bias and ctx.needs_input_grad[1]:
             gb = ck.bias_grad(gy, gy.shape[4])
         return gw, gb, None, gx
@@ -326,6 +404,14 @@ class ConvTranspose3d(nn.ConvTranspose3d):
         super().__init__(*args, **kwargs)
         self._cache = _PackCache()
         self._cache_b = _PackCache()
+        self._spatial = None
+
+    def set_spatial(self, ctx) -> None:
+        self._spatial = ctx
+
+    def _w(self) -> torch.Tensor:
+        k = getattr(self._spatial, "lead_swap", None)
+        return self.weight if k is None else self.weight.transpose(2, k)
 
     def _kernel_ok(self) -> bool:
         return (self.kernel_size == (2, 2, 2) and self.stride == (2, 2, 2) and self.padding == (0, 0, 0)
@@ -336,5 +422,8 @@ class ConvTranspose3d(nn.ConvTranspose3d):
         if use_cuda_kernels(x):
             if not self._kernel_ok() or output_size is not None:
                 raise NotImplementedError(f"sm_100a transposed-conv kernel covers k=2, s=2, no padding; got {self}")
-            return from_vm(_ConvTFn.apply(self.weight, self.bias, self, to_vm(x)))
+            return from_vm(_ConvTFn.apply(self._w(), self.bias, self, to_vm(x)))
+        if getattr(self._spatial, "lead_swap", None) is not None:
+            return F.conv_transpose3d(x, self._w(), self.bias, self.stride, self.padding, self.output_padding,
+                                      self.groups, self.dilation)
         return super().forward(x, output_size)

@@ -84,9 +84,15 @@ def pack_conv3(w: torch.Tensor, src_c: Sequence[int], real_c: Sequence[int], wan
     positions are never written. ``src_c`` are the (padded) channel counts of the concatenated sources,
     ``real_c`` the channels of the weight that belong to each.
     """
-    co, ci = w.shape[:2]
     a = _lib.SbPackArgs()
     wc = w.detach().contiguous().float()
+    fill_pack_args(a, wc, src_c, real_c, want)
+    _lib.check(_lib.lib().sb_pack_conv3(C.byref(a), _lib.stream_ptr()), "sb_pack_conv3")
+
+
+def fill_pack_args(a, wc: torch.Tensor, src_c: Sequence[int], real_c: Sequence[int], want: dict) -> None:
+    """Describe one packing job: ``wc`` is the contiguous fp32 weight, ``want`` the layouts to write."""
+    co, ci = wc.shape[:2]
     a.w = wc.data_ptr()
     a.cout, a.cin = co, ci
     a.real0, a.pad0 = (real_c[0], src_c[0]) if len(src_c) > 1 else (ci, ci)
@@ -96,7 +102,6 @@ def pack_conv3(w: torch.Tensor, src_c: Sequence[int], real_c: Sequence[int], wan
     for name in ("fwd", "fwd_kd", "dgrad", "dgrad_kd"):
         t = want.get(name)
         setattr(a, name, t.data_ptr() if t is not None else None)
-    _lib.check(_lib.lib().sb_pack_conv3(C.byref(a), _lib.stream_ptr()), "sb_pack_conv3")
 
 
 def bias_grad(gy: torch.Tensor, n_out: int) -> torch.Tensor:

@@ -73,3 +73,35 @@ def bump_weights_epoch() -> None:
 
 def weights_epoch() -> int:
     return _weights_epoch[0]
+
+
+# Parameters whose ``.grad`` is a view into a flat gradient buffer (set up by the fused optimizer) are marked
+# with this attribute; the convolution backward passes then add their weight gradient straight into that view
+# (no temporary tensor, no autograd accumulation kernel) and tell the listeners below that it is there.
+FLAT_GRAD_ATTR = "_sb_flat_grad"
+_grad_written_listeners = []
+
+
+def direct_grad_target(param):
+    """The flat-buffer gradient view of ``param`` when the kernels may accumulate into it directly, else None."""
+    if not getattr(param, FLAT_GRAD_ATTR, False):
+        return None
+    g = param.grad
+    if g is None or g.dtype != torch.float32 or not g.is_contiguous() or g.shape != param.shape:
+        return None
+    return g
+
+
+def add_grad_written_listener(fn) -> None:
+    _grad_written_listeners.append(fn)
+
+
+def remove_grad_written_listener(fn) -> None:
+    if fn in _grad_written_listeners:
+        _grad_written_listeners.remove(fn)
+
+
+def notify_grad_written(param) -> None:
+    """Called by a backward pass that wrote ``param.grad`` itself (autograd's accumulate hooks do not fire then)."""
+    for fn in list(_grad_written_listeners):
+        fn(param)

@@ -16,7 +16,7 @@ from typing import Iterable, Optional
 import torch
 
 from . import _lib
-from .layout import bump_weights_epoch
+from .layout import FLAT_GRAD_ATTR, bump_weights_epoch
 
 _P = C.c_void_p
 _lib.register("sb_opt_blocks", [C.c_longlong], C.c_int)
@@ -47,6 +47,7 @@ class FlatBuffers:
             view.copy_(p.data)
             p.data = view
             p.grad = self.grad[o:o + p.numel()].view_as(p)
+            setattr(p, FLAT_GRAD_ATTR, True)
 
     def rehome_grad(self, new_grad: torch.Tensor) -> None:
         """Move the gradient buffer into ``new_grad`` (e.g. peer-visible memory) and re-point every ``.grad``."""
@@ -168,4 +169,6 @@ class FusedClipAdam(torch.optim.Adam):
                                   max_norm, self._norm.data_ptr(), float(self.reduce_scale), s), "sb_adam_step")
         self._step_t.fill_(float(self._steps))
         bump_weights_epoch()
+        from .conv3d import repack_all
+        repack_all()  # one launch refreshes the bf16 operand copies of every convolution for the next step
         return None

@@ -37,13 +37,15 @@ class FusedAllReduce:
         self.ctas, self.wait_seconds = ctas, wait_seconds
         self._bufs, self._flags = self.data.ptr_array(), self.flags.ptr_array()
 
-    def all_reduce_(self, offset: int = 0, count: int = None, scale: float = 1.0) -> None:
-        """Sum elements ``[offset, offset+count)`` of every rank's buffer in place (result x ``scale``)."""
+    def all_reduce_(self, offset: int = 0, count: int = None, scale: float = 1.0, ctas: int = None) -> None:
+        """Sum elements ``[offset, offset+count)`` of every rank's buffer in place (result x ``scale``).
+        ``ctas`` overrides the grid size of this call (0 / None: the full-width default)."""
         count = self.numel - offset if count is None else count
         self.epoch += 1
         status = _lib.status_tensor(self.grad.device)
         _lib.check(_lib.lib().sb_grad_allreduce(self._bufs, self._flags, self.rank, self.world, offset, count,
-                                                self.epoch, float(scale), self.ctas, float(self.wait_seconds),
+                                                self.epoch, float(scale), int(ctas if ctas else self.ctas),
+                                                float(self.wait_seconds),
                                                 status.data_ptr(), _lib.stream_ptr()), "sb_grad_allreduce")
 
     def close(self) -> None:

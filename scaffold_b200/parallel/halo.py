@@ -1,4 +1,6 @@
-"""Fused depth-halo exchange over peer memory for a volume split along D.
+"""Fused halo exchange over peer memory for a volume split along one axis (the kernels' depth axis;
+a volume split along H or W reaches this module with that axis already exchanged with depth, see
+``SpatialContext.lead_swap``).
 
 ``HaloChannel`` owns, per rank, a landing arena and a block of flag words that
 the spatial neighbours can address (:class:`PeerBuffer`). A halo exchange is one
@@ -53,7 +55,7 @@ class Landing:
 class HaloChannel:
     def __init__(self, layout, group, arena_mb: int = 256, wait_seconds: float = 2.0):
         if not self.eligible(layout):
-            raise ValueError("the fused halo channel handles a volume split along depth (dim 2) only")
+            raise ValueError("the fused halo channel handles a volume split along exactly one axis")
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -68,10 +70,8 @@ class HaloChannel:
 
     @staticmethod
     def eligible(layout) -> bool:
-        if 2 not in layout.shard_dim:
-            return False
-        k = layout.shard_dim.index(2)
-        return layout.num_shards[k] >= 2 and all(n == 1 for i, n in enumerate(layout.num_shards) if i != k)
+        """Exactly one split axis: the ranks of the spatial group are then the line of neighbours along it."""
+        return sum(1 for n in layout.num_shards if n > 1) == 1
 
     def flag_addr(self, rank: int, slot: int, face: int) -> int:
         return self.flags.ptrs[rank] + 4 * (slot * 2 + face)

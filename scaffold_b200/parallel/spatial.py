@@ -13,6 +13,13 @@ Transport: ``torch.distributed`` point-to-point (gloo on CPU, NCCL on GPU) of
 contiguous boundary slabs. On a single-node NVLink box the CUDA path can use
 peer memory instead (``halo_backend="fused"``, :mod:`scaffold_b200.parallel.peer`).
 
+Any single split axis runs the fused (in-kernel) halo: the kernels fold the halo of their depth
+axis, so when the volume is split along H or W instead, the model works in *kernel space*, the
+volume with that axis exchanged with depth (``lead_swap``). Convolution, pooling, normalisation
+and the voxel-wise loss are symmetric under such an exchange once the weights' tap axes are
+exchanged the same way, so the modules read their parameters through a transposed view and the
+state dict keeps the ordinary layout. ``dims`` / ``neighbours`` below speak kernel space.
+
 GroupNorm statistics are global over the volume by default (``gn_stats:
 global``): per-(sample, group) count/sum/sumsq (CPU) or Welford partials (CUDA)
 are combined over the spatial group, so a sharded run normalises exactly like
@@ -35,9 +42,16 @@ class SpatialContext:
         self.group = layout.spatial_group
         self.gn_global = gn_stats == "global"
         self.halo_backend = halo_backend
-        self.dims: List[int] = layout.sharded_dims()  # tensor dims (NCDHW numbering) that are split
+        split = layout.sharded_dims()  # tensor dims (NCDHW numbering) of the volume that are split
         self.halo_channel = None
         self.stats_channel = None
+        # One split axis other than depth on the kernel path: exchange it with depth (see the module docstring).
+        self.lead_swap: Optional[int] = None
+        fused_ok = (halo_backend == "fused" and self.size > 1 and torch.cuda.is_available()
+                    and dist.is_initialized() and dist.get_backend() == "nccl")
+        if fused_ok and len(split) == 1 and split[0] != 2:
+            self.lead_swap = split[0]
+        self.dims: List[int] = [2] if self.lead_swap is not None else split  # kernel-space dims that are split
         if (halo_backend == "fused" and self.size > 1 and self.size <= 8 and self.gn_global
                 and torch.cuda.is_available() and dist.get_backend() == "nccl"):
             from .halo import StatsChannel
@@ -54,8 +68,24 @@ class SpatialContext:
         return t
 
     # -- halo exchange -------------------------------------------------------------
+    def volume_dim(self, dim: int) -> int:
+        """Axis of the stored volume behind kernel-space axis ``dim``."""
+        k = self.lead_swap
+        if k is None:
+            return dim
+        return k if dim == 2 else (2 if dim == k else dim)
+
+    def to_kernel_space(self, t: torch.Tensor, first_spatial: int = 2) -> torch.Tensor:
+        """Exchange the split axis with depth (a view); ``first_spatial`` is the position of D in ``t``."""
+        if self.lead_swap is None:
+            return t
+        return t.transpose(first_spatial, first_spatial + self.lead_swap - 2)
+
+    from_kernel_space = to_kernel_space  # the exchange is its own inverse
+
     def neighbours(self, dim: int) -> Tuple[Optional[int], Optional[int]]:
-        return self.layout.neighbour(dim, -1), self.layout.neighbour(dim, +1)
+        d = self.volume_dim(dim)
+        return self.layout.neighbour(d, -1), self.layout.neighbour(d, +1)
 
     def _exchange(self, send_lo: torch.Tensor, send_hi: torch.Tensor, dim: int):
         """Send my low/high boundary slabs to the -/+ neighbours; returns what they sent (zeros at the boundary)."""

@@ -73,9 +73,11 @@ class TrainEngine:
                     logits = self.model(images)
         with region("calculate_loss"):
             if fused:
+                if self.spatial is not None and self.spatial.lead_swap is not None:
+                    masks = self.spatial.to_kernel_space(masks, first_spatial=1).contiguous()  # as the logits are
                 loss, ce, fg = L.segmentation_loss_fused(logits_vm, masks, self.n_classes, self.class_weights,
                                                          self.spatial)
-                return loss, ce, fg, logits_vm
+                return loss, ce, fg, (logits_vm, masks)
             with torch.autocast(self.device.type, enabled=False):
                 loss, ce, fg = L.segmentation_loss_reference(logits, masks, self.n_classes, self.class_weights,
                                                              self.spatial)
@@ -128,6 +130,7 @@ class TrainEngine:
         images, masks = self.to_device(images, masks)
         loss, ce, fg, logits = self.forward_loss(images, masks)
         if self.fused_loss:
+            logits, masks = logits  # kernel-space pair of the fused path
             dice = L.hard_dice_fused(logits, masks, self.n_classes, self.spatial)
         else:
             dice = L.hard_dice_reference(logits.float(), masks, self.n_classes, self.spatial)

@@ -189,6 +189,9 @@ class Trainer:
         local = [int(cfg.vol_size)] * 3
         for n, d in zip(shards, dims):
             local[d - 2] = -(-local[d - 2] // n)
+        k = getattr(self.spatial, "lead_swap", None)
+        if k is not None:  # the model works with the split axis exchanged with depth
+            local[0], local[k - 2] = local[k - 2], local[0]
         try:
             rows = kernel_selection(self.model, int(cfg.local_batch_size), local, self.spatial)
             self.log.info("kernel selection (local volume %s, batch %s):\n%s", "x".join(map(str, local)),

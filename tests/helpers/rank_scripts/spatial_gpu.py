@@ -28,7 +28,8 @@ shards[split_dim - 2] = 2
 layout = ParallelLayout(shards, (2, 3, 4), world, rank)
 spatial = SpatialContext(layout, gn_stats="global", halo_backend=halo_backend)
 if halo_backend == "fused":
-    assert spatial.halo_channel is not None
+    assert spatial.halo_channel is not None and spatial.stats_channel is not None
+    assert spatial.lead_swap == (None if split_dim == 2 else split_dim)
 
 torch.manual_seed(0)
 n_classes = 5
@@ -48,6 +49,8 @@ def step(net, xin, yin, sp):
     net.zero_grad(set_to_none=True)
     with torch.autocast("cuda", dtype=torch.bfloat16):
         logits = net.forward_padded_logits(xin)
+    if sp is not None:  # the logits are in kernel space (split axis exchanged with depth); so must the labels be
+        yin = sp.to_kernel_space(yin, first_spatial=1).contiguous()
     loss, ce, fg = L.segmentation_loss_fused(logits, yin, n_classes, None, sp)
     loss.backward()
     return loss.detach(), [p.grad.detach().float().clone() for p in net.parameters()]

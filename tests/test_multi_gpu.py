@@ -28,7 +28,7 @@ def test_fused_allreduce_matches_nccl_on_two_gpus():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("split_dim,halo", [(2, "nccl"), (4, "nccl"), (2, "fused")])
+@pytest.mark.parametrize("split_dim,halo", [(2, "nccl"), (4, "nccl"), (2, "fused"), (3, "fused"), (4, "fused")])
 def test_two_spatial_shards_match_the_whole_volume_on_gpu(split_dim, halo):
     proc = _torchrun(ROOT / "tests" / "helpers" / "rank_scripts" / "spatial_gpu.py", 2, [str(split_dim), halo])
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
