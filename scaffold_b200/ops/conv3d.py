@@ -88,7 +88,8 @@ class _PackCache:
         self._bufs = {}       # persistent operand buffers (padding positions stay zero)
 
     def _sync(self, w: torch.Tensor):
-        key = (w.data_ptr(), w._version, w.device, weights_epoch())
+        # strides: the same parameter may be read through a tap-transposed view (sharded runs) or directly
+        key = (w.data_ptr(), w._version, w.device, weights_epoch(), tuple(w.stride()))
         if key != self._key:
             self._key = key
             self._vals = {}

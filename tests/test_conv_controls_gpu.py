@@ -1,0 +1,166 @@
+"""More bitwise standards and their negative controls: transposed-convolution tap order, weight-gradient
+slot order, real layer widths, the one-launch repack, gradients written straight into the flat buffer, and
+activation checkpointing on the kernel path."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from test_conv_kernels import ncdhw, ndhwc, tri
+
+pytestmark = pytest.mark.gpu
+
+
+def _ck():
+    from scaffold_b200.ops import _lib, conv_kernels as ck
+    return _lib, ck
+
+
+def test_negative_control_convT_with_permuted_taps_differs():
+    """A transposed convolution whose (kd, kh, kw) taps are packed in another order must fail the bitwise check."""
+    _lib, ck = _ck()
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = tri((1, 64, 4, 8, 16), g)
+    wt = tri((64, 32, 2, 2, 2), g, density=0.7)
+    ref = F.conv_transpose3d(x.double(), wt.double(), stride=2).round().to(torch.bfloat16).double()
+    good = ck.convT_fwd(ndhwc(x), ck.pack_weight_convT_fwd(wt), 32, None)
+    for perm in ((0, 1, 3, 2, 4), (0, 1, 4, 3, 2), (0, 1, 2, 4, 3)):  # swap kd/kh, kd/kw, kh/kw
+        bad = ck.convT_fwd(ndhwc(x), ck.pack_weight_convT_fwd(wt.permute(*perm).contiguous()), 32, None)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        assert not torch.equal(ncdhw(bad), ref), perm
+    assert torch.equal(ncdhw(good), ref)
+    flipped = ck.convT_fwd(ndhwc(x), ck.pack_weight_convT_fwd(wt.flip(2, 3, 4)), 32, None)
+    torch.cuda.synchronize()
+    assert not torch.equal(ncdhw(flipped), ref)
+
+
+def test_negative_control_wgrad_lands_in_the_right_tap_and_channel_slots():
+    """A one-hot gradient and a one-hot input make exactly one (co, ci, tap) entry non-zero: its position is
+    checked directly, and a transposed or tap-mirrored result would put it elsewhere."""
+    _lib, ck = _ck()
+    n, d, h, w, cin, cout = 1, 4, 16, 32, 64, 64
+    for (co, ci, (dz, dy, dx)) in ((5, 40, (1, 0, -1)), (63, 0, (-1, 1, 1)), (17, 17, (0, 0, 0))):
+        x = torch.zeros(n, cin, d, h, w, device="cuda")
+        gy = torch.zeros(n, cout, d, h, w, device="cuda")
+        vz, vy, vx = 2, 7, 13
+        gy[0, co, vz, vy, vx] = 1.0
+        x[0, ci, vz + dz, vy + dy, vx + dx] = 1.0   # y[v] reads x[v + tap - 1]: tap index = offset + 1
+        dw = torch.full((cout, cin, 3, 3, 3), float("nan"), device="cuda")
+        ck.conv_wgrad(ndhwc(gy), [ndhwc(x)], 3, dw)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        want = torch.zeros_like(dw)
+        want[co, ci, dz + 1, dy + 1, dx + 1] = 1.0
+        assert torch.equal(dw, want)
+        assert not torch.equal(dw, want.flip(2, 3, 4)) or (dz, dy, dx) == (0, 0, 0)
+        if co != ci:
+            assert not torch.equal(dw, want.transpose(0, 1))
+
+
+@pytest.mark.parametrize("cin,cout,dims", [(128, 64, (8, 64, 64)), (256, 128, (6, 32, 32)), (64, 128, (8, 32, 64)),
+                                           (512, 256, (4, 16, 16))], ids=lambda v: str(v))
+def test_real_layer_widths_forward_dgrad_wgrad_bitwise(cin, cout, dims):
+    _lib, ck = _ck()
+    g = torch.Generator(device="cuda").manual_seed(41)
+    d, h, w = dims
+    x = tri((1, cin, d, h, w), g, density=0.25)
+    gy = tri((1, cout, d, h, w), g, density=0.25)
+    wt = tri((cout, cin, 3, 3, 3), g, density=0.25)
+    xr, wr = x.double().requires_grad_(True), wt.double().requires_grad_(True)
+    ref = F.conv3d(xr, wr, padding=1)
+    ref.backward(gy.double())
+    (y,) = ck.conv_same([ndhwc(x)], ck.pack_weight_fwd(wt), 3, [cout])
+    (gx,) = ck.conv_same([ndhwc(gy)], ck.pack_weight_dgrad(wt), 3, [cin])
+    dw = torch.full_like(wt, float("nan"))
+    ck.conv_wgrad(ndhwc(gy), [ndhwc(x)], 3, dw)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert torch.equal(ncdhw(y), ref.detach().round().to(torch.bfloat16).double())
+    assert torch.equal(ncdhw(gx), xr.grad.round().to(torch.bfloat16).double())
+    assert torch.equal(dw.double(), wr.grad.round())
+
+
+def _tiny_model(width=32, layers=2, classes=5):
+    from scaffold_b200.models.unet import UNet
+    torch.manual_seed(0)
+    return UNet(3, classes, layers=layers, base_width=width).cuda()
+
+
+def test_one_launch_repack_and_direct_gradients_match_the_lazy_autograd_path():
+    """Model ``a`` trains through FusedClipAdam (flat buffers: weight gradients are added straight into the flat
+    buffer, every 3x3x3 pack is refreshed by ONE launch after the update); model ``b`` gets its gradients through
+    autograd. Same kernels in the same order: the gradients are bitwise equal, and after the update the batched
+    packs give the same logits as a fresh model that packs the same weights lazily, layer by layer."""
+    from scaffold_b200.ops import _lib, loss as L
+    from scaffold_b200.ops.optim import FusedClipAdam
+    a, b = _tiny_model(), _tiny_model()
+    b.load_state_dict(a.state_dict())
+    opt_a = FusedClipAdam(a.parameters(), lr=1e-3, max_norm=1.0)
+    opt_a.attach()
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.rand((2, 3, 32, 32, 32), generator=g, device="cuda")
+    y = torch.randint(0, 5, (2, 32, 32, 32), generator=g, device="cuda", dtype=torch.int16)
+
+    def fwd_bwd(model):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            logits = model.forward_padded_logits(x)
+        loss, _, _ = L.segmentation_loss_fused(logits, y, 5)
+        loss.backward()
+        return logits.detach()
+
+    opt_a.zero_grad()
+    fwd_bwd(a)
+    fwd_bwd(b)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    for (name, pa), pb in zip(a.named_parameters(), b.parameters()):
+        assert torch.equal(pa.grad, pb.grad), name
+    opt_a.step()                     # update + the one-launch repack
+    c = _tiny_model()
+    c.load_state_dict(a.state_dict())
+    n0 = _lib.launch_count()
+    opt_a.zero_grad()
+    la = fwd_bwd(a)
+    n_a = _lib.launch_count() - n0
+    n0 = _lib.launch_count()
+    lc = fwd_bwd(c)
+    n_c = _lib.launch_count() - n0
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert torch.equal(la, lc)
+    assert n_a < n_c                 # no per-layer packing launches on the model whose packs were batched
+
+
+def test_activation_checkpointing_on_the_kernel_path_gives_the_same_gradients():
+    from scaffold_b200.ops import _lib, loss as L
+    a, b = _tiny_model(), _tiny_model()
+    b.load_state_dict(a.state_dict())
+    b.use_checkpointing()
+    g = torch.Generator(device="cuda").manual_seed(8)
+    x = torch.rand((1, 3, 32, 32, 32), generator=g, device="cuda")
+    y = torch.randint(0, 5, (1, 32, 32, 32), generator=g, device="cuda", dtype=torch.int16)
+    grads = []
+    for model in (a, b):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            logits = model.forward_padded_logits(x)
+        loss, _, _ = L.segmentation_loss_fused(logits, y, 5)
+        loss.backward()
+        grads.append([p.grad.clone() for p in model.parameters()])
+    torch.cuda.synchronize()
+    _lib.check_status()
+    for ga, gb in zip(*grads):
+        assert torch.equal(ga, gb)  # recomputation replays the same deterministic kernels
+
+
+def test_kernel_selection_report_lists_every_layer():
+    from scaffold_b200.ops.selection import format_selection, kernel_selection
+    model = _tiny_model(width=64, layers=2)
+    rows = kernel_selection(model, 2, (64, 64, 64))
+    names = [r["layer"] for r in rows]
+    assert "down_list.0.double_conv.0" in names and "up_list.2.conv" in names
+    by = {r["layer"]: r for r in rows}
+    assert by["down_list.0.double_conv.3"]["fwd"] == "conv_plane3"
+    assert by["down_list.0.double_conv.0"]["dgrad"] == "-"
+    assert by["up_list.0.up"]["fwd"].startswith("igemm")
+    text = format_selection(rows, {"halo_exchange_effective": "none"})
+    assert "weight-grad" in text and "halo_exchange_effective: none" in text
