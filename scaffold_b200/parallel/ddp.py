@@ -76,7 +76,8 @@ class GradReducer:
             members.append(i)
             lo = flat.offsets[i]
             if hi - lo >= bucket_elems or i == 0:
-                b = {"lo": lo, "hi": hi, "n": len(members), "pending": len(members), "launched": False}
+                b = {"lo": lo, "hi": hi, "n": len(members), "pending": len(members), "launched": False,
+                     "seen": set()}
                 for m in members:
                     self._bucket_of[id(flat.params[m])] = b
                 self._buckets.append(b)
@@ -89,9 +90,13 @@ class GradReducer:
         add_grad_written_listener(self._on_grad)  # gradients the kernels wrote into the flat buffer themselves
 
     def _on_grad(self, p) -> None:
+        """One gradient of this step is in the flat buffer (its kernels are enqueued on the current stream).
+        A parameter is counted once per step: autograd may also run its accumulate hook for a weight whose
+        gradient the convolution wrote directly (``notify_grad_written`` came first, when the data was there)."""
         b = self._bucket_of.get(id(p))
-        if b is None or b["launched"]:
+        if b is None or b["launched"] or id(p) in b["seen"]:
             return
+        b["seen"].add(id(p))
         b["pending"] -= 1
         if b["pending"] == 0:
             self._launch(b)
@@ -117,6 +122,7 @@ class GradReducer:
         torch.cuda.current_stream().wait_stream(self._comm)
         for b in self._buckets:
             b["pending"], b["launched"] = b["n"], False
+            b["seen"].clear()
 
     @property
     def effective_backend(self) -> str:

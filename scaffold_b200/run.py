@@ -113,6 +113,7 @@ def worker(run_dict: Dict[str, Any]) -> Dict[str, Any]:
     D.barrier()
 
     result = dict(summary)
+    result["dataset_path"] = str(config.dataset_dir)  # the resolved dataset (cache entry) this run trained on
     if rank == 0:
         fom = figure_of_merit(Path(config.run_dir) / "train_stats.csv", float(config.target_dice))
         result.update(fom)

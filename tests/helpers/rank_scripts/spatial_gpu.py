@@ -1,6 +1,6 @@
 """Rank script (2 GPUs): a U-Net step on a volume split over two spatial shards vs the unsharded step.
 
-usage: spatial_gpu.py <split_dim 2|3|4> [nccl|fused]
+usage: spatial_gpu.py <split_dim 2|3|4 | shards "a,b,c"> [nccl|fused]   (world = product of the shard counts)
 Both ranks hold the same weights. Each runs forward + fused loss + backward on its half; gradients are summed
 over the shards. Rank 0 then repeats the step on the whole volume without sharding and compares loss and grads.
 """
@@ -21,15 +21,23 @@ from scaffold_b200.parallel.layout import ParallelLayout  # noqa: E402
 from scaffold_b200.parallel.spatial import SpatialContext  # noqa: E402
 from scaffold_b200.run import attach_spatial  # noqa: E402
 
-split_dim = int(sys.argv[1]) if len(sys.argv) > 1 else 2
+spec = sys.argv[1] if len(sys.argv) > 1 else "2"
 halo_backend = sys.argv[2] if len(sys.argv) > 2 else "nccl"
-shards = [1, 1, 1]
-shards[split_dim - 2] = 2
+if "," in spec:
+    shards = [int(v) for v in spec.split(",")]
+    split_dim = None
+else:
+    split_dim = int(spec)
+    shards = [1, 1, 1]
+    shards[split_dim - 2] = 2
 layout = ParallelLayout(shards, (2, 3, 4), world, rank)
 spatial = SpatialContext(layout, gn_stats="global", halo_backend=halo_backend)
+single_axis = sum(1 for v in shards if v > 1) == 1
 if halo_backend == "fused":
-    assert spatial.halo_channel is not None and spatial.stats_channel is not None
-    assert spatial.lead_swap == (None if split_dim == 2 else split_dim)
+    assert spatial.stats_channel is not None
+    assert (spatial.halo_channel is not None) == single_axis  # several split axes: slabs travel through NCCL
+    if split_dim is not None:
+        assert spatial.lead_swap == (None if split_dim == 2 else split_dim)
 
 torch.manual_seed(0)
 n_classes = 5
@@ -38,9 +46,10 @@ S = 64
 g = torch.Generator(device="cuda").manual_seed(5)
 x = torch.rand((1, 3, S, S, S), generator=g, device=dev)
 y = torch.randint(0, n_classes, (1, S, S, S), generator=g, device=dev, dtype=torch.int16)
-half = S // 2
 sl = [slice(None)] * 5
-sl[split_dim] = slice(rank * half, (rank + 1) * half)
+for k, (dim, nsh) in enumerate(zip((2, 3, 4), shards)):
+    ext = S // nsh
+    sl[dim] = slice(layout.shard_ind[k] * ext, (layout.shard_ind[k] + 1) * ext)
 xl = x[tuple(sl)].contiguous()
 yl = y[tuple(sl[:1] + sl[2:])].contiguous()
 

@@ -49,3 +49,20 @@ def test_bucketed_gradient_reduction_under_backward_matches_the_single_call(back
         assert res["same"][0].split()[0] == "True", res
     else:
         assert float(res["same"][0].split()[1]) < 1e-4, res
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs eight GPUs")
+def test_eight_shards_on_three_axes_match_the_whole_volume_on_gpu():
+    proc = _torchrun(ROOT / "tests" / "helpers" / "rank_scripts" / "spatial_gpu.py", 8, ["2,2,2", "fused"], timeout=600)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
+    res = results(proc.stdout)
+    a, b = (float(v) for v in res["loss"][0].split())
+    assert abs(a - b) <= 2e-3 * max(1.0, abs(b)), res
+    assert float(res["grad_rel"][0]) < 0.08, res
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 8, reason="needs eight GPUs")
+def test_fused_allreduce_matches_nccl_on_eight_gpus():
+    proc = _torchrun(ROOT / "tests" / "helpers" / "rank_scripts" / "fused_allreduce_gpu.py", 8, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    assert results(proc.stdout)["equal"] == ["True"]
