@@ -424,6 +424,7 @@ using namespace sb;
 namespace sb {
 int conv_plane_launch(const SbConvArgs* a, cudaStream_t stream);
 int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream);
+int conv_plane3_gn_splits(const SbConvArgs* a);
 int conv_small_launch(const SbConvArgs* a, cudaStream_t stream);
 long long conv_small_workspace(const SbConvArgs* a);
 }
@@ -431,6 +432,10 @@ long long conv_small_workspace(const SbConvArgs* a);
 // fp32 scratch elements sb_conv_fwd wants for this call (0: none)
 extern "C" long long sb_conv_fwd_workspace(const SbConvArgs* a) {
   return a->force_plain == 0 ? conv_small_workspace(a) : 0;
+}
+
+extern "C" int sb_conv_gn_splits(const SbConvArgs* a) {
+  return a->force_plain == 0 ? conv_plane3_gn_splits(a) : 0;
 }
 
 // force_plain: 0 = automatic (8 x 8 plane kernel, kd-fused or plane-walk kernel when the shape is eligible, else
@@ -442,6 +447,7 @@ extern "C" int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream) {
     if (sm >= 0) return sm;
     const int p3 = conv_plane3_launch(a, stream);
     if (p3 >= 0) return p3;
+    if (a->gn_part != nullptr) return SB_ERR_SHAPE;  // statistics come from the kd-fused kernel only
     if (a->wpack == nullptr) return SB_ERR_SHAPE;  // only the kd-ordered weights were given
     const int prc = conv_plane_launch(a, stream);
     if (prc >= 0) return prc;

@@ -54,6 +54,10 @@ struct Plane3Params {
   const float* bias;
   uint32_t* status;
   unsigned long long* stall;  // optional stall counters (clock ticks summed over CTAs), null = off
+  float* gn_part;   // optional GroupNorm partials of the output: [N][jobs per sample and channel tile][G][3]
+  int gn_groups;    // G
+  int gn_cg;        // channels per group (4 .. BN, divides BN)
+  int gn_splits;    // groups_d * tiles_h * tiles_w * 4 (one partial per epilogue warp)
 };
 
 struct P3Job { int co0, h0, w0, d0, n; };
@@ -68,7 +72,9 @@ __device__ __forceinline__ P3Job p3_decode(const Plane3Params& p, int job) {
   return j;
 }
 
-template <int TD>
+// STATS: the epilogue also writes GroupNorm partials (forward passes only; the variant without them keeps the
+// register count low enough for small co-resident kernels, e.g. the overlapped gradient reduction, during backward)
+template <int TD, bool STATS>
 __global__ void __launch_bounds__(224, 2) conv_plane3_kernel(const __grid_constant__ Plane3Params p) {
   constexpr int planes = TD + 2;
   extern __shared__ uint8_t smem_raw[];
@@ -81,6 +87,7 @@ __global__ void __launch_bounds__(224, 2) conv_plane3_kernel(const __grid_consta
   __shared__ uint64_t tempty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_s;
+  __shared__ float gn_s[4][33];  // per epilogue warp: 16 x (sum, sum of squares) over 4-channel runs + voxel count
   volatile uint32_t* abort_flag = &abort_s;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -307,6 +314,14 @@ __global__ void __launch_bounds__(224, 2) conv_plane3_kernel(const __grid_consta
       tc_fence_after();
       const P3Job jc = p3_decode(p, job);
       const int h = jc.h0 + rh, w = jc.w0 + rw;
+      // GroupNorm statistics of what this job stores (optional): per thread, sums over runs of 4 channels
+      float gsum[16], gsq[16];
+      float gcnt = 0.f;
+      constexpr bool stats = STATS;
+      if (stats) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { gsum[i] = 0.f; gsq[i] = 0.f; }
+      }
       for (int t = 0; t < TD; ++t) {
         const int d = jc.d0 + t;
         const bool valid = h < p.H && w < p.W && d < p.D;
@@ -321,7 +336,11 @@ __global__ void __launch_bounds__(224, 2) conv_plane3_kernel(const __grid_consta
         }
         const uint32_t acc_i = buf * TD + t;
         const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + acc_i * p.BN;
-        for (int c0 = 0; c0 < p.BN; c0 += 16) {
+        if (stats && valid) gcnt += 1.f;
+#pragma unroll
+        for (int ci = 0; ci < 4; ++ci) {
+          const int c0 = ci * 16;
+          if (c0 >= p.BN) break;
           uint32_t v[16];
           tmem_ld_32x16(tbase + c0, v);
           tmem_ld_wait();
@@ -339,6 +358,17 @@ __global__ void __launch_bounds__(224, 2) conv_plane3_kernel(const __grid_consta
               }
               o[g].x = pack_bf16x2(f[0], f[1]); o[g].y = pack_bf16x2(f[2], f[3]);
               o[g].z = pack_bf16x2(f[4], f[5]); o[g].w = pack_bf16x2(f[6], f[7]);
+              if (stats) {
+                // the values as stored (bf16-rounded): the statistics must describe the tensor the next pass reads
+                const uint32_t w4[4] = {o[g].x, o[g].y, o[g].z, o[g].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float lo = __uint_as_float(w4[e] << 16), hi = __uint_as_float(w4[e] & 0xffff0000u);
+                  const int run = ci * 4 + g * 2 + (e >> 1);
+                  gsum[run] += lo + hi;
+                  gsq[run] += lo * lo + hi * hi;
+                }
+              }
             }
             if (slab) {
               if (col0 < p.width0 + p.width1) {
@@ -362,6 +392,43 @@ __global__ void __launch_bounds__(224, 2) conv_plane3_kernel(const __grid_consta
             }
           }
         }
+      }
+      if (stats) {
+        // warp sums; every epilogue warp owns 32 rows of the tile and writes its own partial (no cross-warp barrier)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+#pragma unroll
+          for (int o2 = 16; o2 > 0; o2 >>= 1) {
+            gsum[i] += __shfl_xor_sync(0xffffffffu, gsum[i], o2);
+            gsq[i] += __shfl_xor_sync(0xffffffffu, gsq[i], o2);
+          }
+        }
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) gcnt += __shfl_xor_sync(0xffffffffu, gcnt, o2);
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) { gn_s[q][2 * i] = gsum[i]; gn_s[q][2 * i + 1] = gsq[i]; }
+          gn_s[q][32] = gcnt;
+        }
+        __syncwarp();
+        const int groups_here = p.BN / p.gn_cg;      // groups this channel tile covers (at most 16)
+        if (lane < groups_here) {
+          const int runs = p.gn_cg / 4;
+          float s1 = 0.f, s2 = 0.f;
+          for (int r = 0; r < runs; ++r) {
+            s1 += gn_s[q][2 * (lane * runs + r)];
+            s2 += gn_s[q][2 * (lane * runs + r) + 1];
+          }
+          const float n_el = gn_s[q][32] * (float)p.gn_cg;
+          const float mean = n_el > 0.f ? s1 / n_el : 0.f;
+          const float m2 = n_el > 0.f ? fmaxf(s2 - s1 * mean, 0.f) : 0.f;
+          const int sj = ((jc.d0 / TD * p.tiles_h + jc.h0 / 8) * p.tiles_w + jc.w0 / 16) * 4 + q;
+          const int g_glob = jc.co0 / p.gn_cg + lane;
+          float* dst = p.gn_part + (((long long)jc.n * p.gn_splits + sj) * p.gn_groups + g_glob) * 3;
+          dst[0] = n_el; dst[1] = mean; dst[2] = m2;
+        }
+        __syncwarp();  // gn_s[q] is reused by this warp's next job
       }
       tc_fence_before();
       __syncwarp();
@@ -396,9 +463,10 @@ static int p3_setup() {
   int lim = 0, sms = 0;
   cudaDeviceGetAttribute(&lim, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const void* fns[3] = {(const void*)conv_plane3_kernel<1>, (const void*)conv_plane3_kernel<2>,
-                        (const void*)conv_plane3_kernel<4>};
-  for (int i = 0; i < 3; ++i)
+  const void* fns[6] = {(const void*)conv_plane3_kernel<1, false>, (const void*)conv_plane3_kernel<2, false>,
+                        (const void*)conv_plane3_kernel<4, false>, (const void*)conv_plane3_kernel<1, true>,
+                        (const void*)conv_plane3_kernel<2, true>, (const void*)conv_plane3_kernel<4, true>};
+  for (int i = 0; i < 6; ++i)
     if (cudaFuncSetAttribute(fns[i], cudaFuncAttributeMaxDynamicSharedMemorySize, lim - 2048) != cudaSuccess)
       return SB_ERR_DRIVER;
   g_p3_smem = lim - 2048;
@@ -410,16 +478,16 @@ static int cdiv_p3(int a, int b) { return (a + b - 1) / b; }
 
 // Returns -1 when the call is not eligible (no kd-grouped weights, wide outputs, channel counts that
 // are not multiples of 32); the caller then uses the plane-walk kernel.
-int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream) {
+// Tile shape, job depth and CTA mode of a call (everything the launch and the statistics query share).
+// Returns -1 when the call is not eligible, an SB_ERR_* code on failure, 0 with `p` / `dual` filled otherwise.
+static int p3_plan(const SbConvArgs* a, Plane3Params& p, bool& dual) {
   if (a->ksize != 3 || a->W < 16 || a->H < 8 || a->wpack_kd == nullptr) return -1;
   if (a->cout_pad % 16 != 0 || (a->cout_pad > 64 && a->cout_pad % 64 != 0)) return -1;
   const int cin_tot = a->src_c[0] + a->src_c[1];
   if (a->src_c[0] % P3_BK != 0 || cin_tot % P3_BK != 0) return -1;
   int rc = p3_setup();
   if (rc) return rc;
-  Plane3Params p;
   memset(&p, 0, sizeof(p));
-  const int nsrc = a->src_c[1] > 0 ? 2 : 1;
   p.BN = a->cout_pad > 64 ? 64 : a->cout_pad;
   p.N = a->N; p.D = a->D; p.H = a->H; p.W = a->W;
   p.tiles_h = cdiv_p3(a->H, 8);
@@ -436,7 +504,7 @@ int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream) {
   // (deeper jobs) x the measured preference of the mode (two CTAs per SM gain about 7 % on deep reductions and
   // lose about as much on shallow ones). A small volume with many channels may fill 148 slots but not 296.
   const int cblks_all = cin_tot / P3_BK;
-  bool dual = cblks_all >= 4;
+  dual = cblks_all >= 4;
   int td = 1;
   double best = 0.0;
   for (int mode = 0; mode < 2; ++mode) {
@@ -452,7 +520,6 @@ int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream) {
       if (score > best) { best = score; td = cand; dual = d2; }
     }
   }
-  const int slots = (dual ? 2 : 1) * g_p3_sms;
   p.nsets = dual ? 1 : 2;
   p.nbufs = dual ? 1 : 2;
   p.TD = td;
@@ -460,6 +527,41 @@ int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream) {
   while (p.tmem_cols < p.nbufs * td * p.BN) p.tmem_cols *= 2;
   p.groups_d = cdiv_p3(a->D, td);
   p.num_jobs = a->N * p.groups_d * p.tiles_h * p.tiles_w * p.tiles_co;
+  return 0;
+}
+
+// GroupNorm statistics from the epilogue: one destination, no slab outputs, a group made of whole 4-channel runs
+// that does not straddle channel tiles, at most 16 groups per tile.
+static bool p3_gn_ok(const SbConvArgs* a, const Plane3Params& p) {
+  if (a->gn_groups < 1 || a->dst[1] != nullptr || a->slab_out[0] != nullptr) return false;
+  if (a->dst_c[0] != a->cout_pad || a->cout_pad % a->gn_groups != 0) return false;
+  const int cg = a->cout_pad / a->gn_groups;
+  return cg % 4 == 0 && cg <= p.BN && p.BN % cg == 0 && p.BN / cg <= 16;
+}
+
+int conv_plane3_gn_splits(const SbConvArgs* a) {
+  Plane3Params p;
+  bool dual = false;
+  if (p3_plan(a, p, dual) != 0 || !p3_gn_ok(a, p)) return 0;
+  return p.groups_d * p.tiles_h * p.tiles_w * 4;
+}
+
+int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream) {
+  Plane3Params p;
+  bool dual = false;
+  int rc = p3_plan(a, p, dual);
+  if (rc != 0) return rc;
+  const int cin_tot = a->src_c[0] + a->src_c[1];
+  const int nsrc = a->src_c[1] > 0 ? 2 : 1;
+  const int td = p.TD;
+  const int slots = (dual ? 2 : 1) * g_p3_sms;
+  if (a->gn_part != nullptr) {
+    if (!p3_gn_ok(a, p)) return SB_ERR_SHAPE;
+    p.gn_part = a->gn_part;
+    p.gn_groups = a->gn_groups;
+    p.gn_cg = a->cout_pad / a->gn_groups;
+    p.gn_splits = p.groups_d * p.tiles_h * p.tiles_w * 4;
+  }
   const int budget = dual ? g_p3_smem / 2 - 2048 : g_p3_smem;  // per CTA
   const int a_bytes = p.nsets * (td + 2) * p.a_slot_bytes;
   // weight boxes of a whole kh row (nine taps) when two of them fit: a third of the waits and commits
@@ -536,9 +638,13 @@ int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream) {
     p.wide = 0;
   const int grid = p.num_jobs < slots ? p.num_jobs : slots;
   const size_t smem = (size_t)a_bytes + (size_t)p.b_slots * p.b_slot_bytes + 1024;
-  if (td == 4) conv_plane3_kernel<4><<<grid, 224, smem, stream>>>(p);
-  else if (td == 2) conv_plane3_kernel<2><<<grid, 224, smem, stream>>>(p);
-  else conv_plane3_kernel<1><<<grid, 224, smem, stream>>>(p);
+  if (p.gn_part != nullptr) {
+    if (td == 4) conv_plane3_kernel<4, true><<<grid, 224, smem, stream>>>(p);
+    else if (td == 2) conv_plane3_kernel<2, true><<<grid, 224, smem, stream>>>(p);
+    else conv_plane3_kernel<1, true><<<grid, 224, smem, stream>>>(p);
+  } else if (td == 4) conv_plane3_kernel<4, false><<<grid, 224, smem, stream>>>(p);
+  else if (td == 2) conv_plane3_kernel<2, false><<<grid, 224, smem, stream>>>(p);
+  else conv_plane3_kernel<1, false><<<grid, 224, smem, stream>>>(p);
   sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }

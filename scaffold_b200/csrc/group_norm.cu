@@ -462,6 +462,48 @@ __global__ void __launch_bounds__(GN_THREADS) gn_stats_finalize_kernel(const flo
   }
 }
 
+// The same collapse for MANY partials per (n, g) (the per-warp partials a convolution's epilogue leaves: up to
+// 16K per sample): one block per (n, g); thread t merges partials t, t + 256, ... in order, then a fixed
+// shared-memory tree merges the 256 results (lower index first), so the result is deterministic.
+__global__ void __launch_bounds__(GN_THREADS) gn_stats_finalize_wide_kernel(const float* __restrict__ part,
+                                                                            float* __restrict__ fin, int N, int G,
+                                                                            int nsplit) {
+  __shared__ float s_n[GN_THREADS], s_m[GN_THREADS], s_2[GN_THREADS];
+  const int n = blockIdx.x / G, g = blockIdx.x % G;
+  float gn = 0.f, gm = 0.f, g2 = 0.f;
+  const float* base = part + ((long long)n * nsplit * G + g) * 3;
+  int s = threadIdx.x;
+  // four independent loads in flight per thread; merged in index order
+  for (; s + 3 * GN_THREADS < nsplit; s += 4 * GN_THREADS) {
+    float e[4][3];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float* q = base + (long long)(s + u * GN_THREADS) * G * 3;
+      e[u][0] = q[0]; e[u][1] = q[1]; e[u][2] = q[2];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) chan_merge(gn, gm, g2, e[u][0], e[u][1], e[u][2]);
+  }
+  for (; s < nsplit; s += GN_THREADS) {
+    const float* q = base + (long long)s * G * 3;
+    chan_merge(gn, gm, g2, q[0], q[1], q[2]);
+  }
+  s_n[threadIdx.x] = gn; s_m[threadIdx.x] = gm; s_2[threadIdx.x] = g2;
+  __syncthreads();
+  for (int o = GN_THREADS / 2; o > 0; o >>= 1) {
+    if (threadIdx.x < o) {
+      float an = s_n[threadIdx.x], am = s_m[threadIdx.x], a2 = s_2[threadIdx.x];
+      chan_merge(an, am, a2, s_n[threadIdx.x + o], s_m[threadIdx.x + o], s_2[threadIdx.x + o]);
+      s_n[threadIdx.x] = an; s_m[threadIdx.x] = am; s_2[threadIdx.x] = a2;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    float* dst = fin + ((long long)n * G + g) * 3;
+    dst[0] = s_n[0]; dst[1] = s_m[0]; dst[2] = s_2[0];
+  }
+}
+
 __global__ void __launch_bounds__(GN_THREADS) gn_bwd_finalize_kernel(const float* __restrict__ part,
                                                                      float* __restrict__ fin, int N, int C,
                                                                      int nsplit) {
@@ -620,6 +662,11 @@ extern "C" int sb_gn_share(const float* fin, long long count, void* const* dst, 
 // fin: [N][G][3] (stats) / [N][C][2] (bwd) -- the single-split form the apply / dx kernels merge
 extern "C" int sb_gn_stats_finalize(const float* part, float* fin, int N, int G, int nsplit, cudaStream_t stream) {
   const int warps = N * G;
+  if (nsplit > 1024) {  // a warp per output would walk hundreds of partials per lane: a block per output instead
+    gn_stats_finalize_wide_kernel<<<warps, GN_THREADS, 0, stream>>>(part, fin, N, G, nsplit);
+    sb_count_launch(1);
+    return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+  }
   gn_stats_finalize_kernel<<<(warps * 32 + GN_THREADS - 1) / GN_THREADS, GN_THREADS, 0, stream>>>(part, fin, N, G, nsplit);
   sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;

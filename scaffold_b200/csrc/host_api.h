@@ -58,6 +58,12 @@ typedef struct {
   // fp32 scratch for kernels that split the reduction (conv_small.cu); sb_conv_fwd_workspace() says how much
   float* workspace;
   long long workspace_elems;
+  // GroupNorm statistics of the OUTPUT from the epilogue (kd-fused kernel, one destination): when gn_part is set,
+  // every job also writes (count, mean, M2) of the bf16-rounded values it stored, per group of C / gn_groups
+  // channels, into gn_part[N][splits][gn_groups][3] (splits = sb_conv_gn_splits(); the layout sb_gn_stats writes),
+  // so the normalisation that follows skips its own pass over the tensor.
+  float* gn_part;
+  int gn_groups;
 } SbConvArgs;
 
 // One pass over fp32 3x3x3 weights [cout][cin][27] -> bf16 operand layouts (null = not wanted):
@@ -166,6 +172,8 @@ int sb_gn_bwd_dx(const SbGnArgs* a, cudaStream_t stream);
 
 int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream);
 long long sb_conv_fwd_workspace(const SbConvArgs* a);
+// splits per sample of the statistics the call would write into gn_part; 0 = this call cannot produce them
+int sb_conv_gn_splits(const SbConvArgs* a);
 int sb_convT_fwd(const SbConvTArgs* a, cudaStream_t stream);
 int sb_convT_dgrad(const SbConvTArgs* a, cudaStream_t stream);
 int sb_conv_wgrad(const SbWgradArgs* a, cudaStream_t stream);

@@ -54,6 +54,10 @@ class DoubleConv(nn.Module):
             nn.Identity(),
         )
 
+        # each convolution feeds a GroupNorm: its kernel can hand the statistics over and save that pass
+        self.double_conv[0].gn_groups_hint = group_norm_groups
+        self.double_conv[3].gn_groups_hint = group_norm_groups
+
     @annotate("DoubleConv.forward")
     def forward(self, x):
         return self.double_conv(x)

@@ -55,6 +55,8 @@ class SbConvArgs(C.Structure):
         ("wpack_kd", C.c_void_p),
         ("workspace", C.c_void_p),
         ("workspace_elems", C.c_longlong),
+        ("gn_part", C.c_void_p),
+        ("gn_groups", C.c_int),
     ]
 
 
@@ -141,6 +143,7 @@ _P = C.c_void_p
 _SIGNATURES = {
     "sb_conv_fwd": ([C.POINTER(SbConvArgs), _P], C.c_int),
     "sb_conv_fwd_workspace": ([C.POINTER(SbConvArgs)], C.c_longlong),
+    "sb_conv_gn_splits": ([C.POINTER(SbConvArgs)], C.c_int),
     "sb_pack_conv3": ([C.POINTER(SbPackArgs), _P], C.c_int),
     "sb_pack_conv3_plan": ([C.POINTER(SbPackJob), C.c_int], C.c_longlong),
     "sb_pack_conv3_batch": ([_P, C.c_int, C.c_longlong, _P], C.c_int),

@@ -18,6 +18,7 @@ CUDA path (role of ``_skip_concat``, ScaFFold/unet/unet_parts.py:76-120, and of
 from __future__ import annotations
 
 import ctypes as C
+import os
 import weakref
 from typing import List, Optional, Sequence, Union
 
@@ -28,6 +29,9 @@ import torch.nn.functional as F
 from . import conv_kernels as ck
 from .layout import direct_grad_target, from_vm, notify_grad_written, to_vm, use_cuda_kernels, weights_epoch
 
+
+# A/B switch: "0" keeps the GroupNorm statistics in their own pass instead of the convolution's epilogue
+_GN_FROM_EPILOGUE = os.environ.get("SCAFFOLD_GN_FROM_EPILOGUE", "1") != "0"
 
 _PACK_REGISTRY: "weakref.WeakSet[_PackCache]" = weakref.WeakSet()
 _PACK_PLAN = {"key": None, "table": None, "n": 0, "tiles": 0, "members": []}
@@ -176,8 +180,11 @@ class _ConvSameFn(torch.autograd.Function):
         bpad = None
         if bias is not None:
             bpad = mod._cache_b.get(bias, "b", lambda b: F.pad(b, (0, cout_pad - b.shape[0])).contiguous())
+        sink = []
+        gn = mod.gn_groups_hint if (_GN_FROM_EPILOGUE and ks == 3 and cout_pad == weight.shape[0]) else 0
         (y,) = ck.conv_same(list(fwd_xs if fwd_xs is not None else xs), wf, ks, [cout_pad], bias=bpad,
-                            out_dims=out_dims, in_off=in_off)
+                            out_dims=out_dims, in_off=in_off, gn_groups=gn, gn_sink=sink)
+        mod._gn_partials = sink[0] if sink else None  # picked up by Conv3d.forward, handed to the GroupNorm
         ctx.mod = mod
         ctx.wparam = weight  # the caller's tensor itself: backward may add into its flat-buffer .grad
         ctx.in_off, ctx.in_dims = in_off, in_dims
@@ -243,7 +250,10 @@ class _ConvHaloFn(torch.autograd.Function):
         wf = mod._cache.conv3(weight, src_c, src_c, "fwd", kd)
         cout_pad = wf.shape[1]
         landing = chan.exchange([x[:, 0] for x in xs], [x[:, -1] for x in xs])
-        (y,) = ck.conv_same(list(xs), wf, 3, [cout_pad], halo=landing)
+        sink = []
+        gn = mod.gn_groups_hint if (_GN_FROM_EPILOGUE and cout_pad == weight.shape[0]) else 0
+        (y,) = ck.conv_same(list(xs), wf, 3, [cout_pad], halo=landing, gn_groups=gn, gn_sink=sink)
+        mod._gn_partials = sink[0] if sink else None
         ctx.halo_saved = landing.clone()  # the arena slot is recycled; backward needs the planes again
         ctx.mod, ctx.chan, ctx.src_c = mod, chan, src_c
         ctx.wparam = weight
@@ -291,6 +301,8 @@ class Conv3d(nn.Conv3d):
         self._cache = _PackCache()
         self._cache_b = _PackCache()
         self._spatial = None  # parallel.spatial.SpatialContext when the volume is sharded
+        self.gn_groups_hint = 0   # groups of the GroupNorm that consumes this layer's output (0: none / unknown)
+        self._gn_partials = None  # statistics the last forward kernel produced for that GroupNorm
 
     def set_spatial(self, ctx) -> None:
         self._spatial = ctx
@@ -321,7 +333,11 @@ class Conv3d(nn.Conv3d):
                     f"sm_100a conv kernels cover k in (1,3), stride 1, 'same' zero padding; got {self}")
             y = self._cuda_forward(xs)
             out = from_vm(y)
-            return out if y.shape[4] == self.out_channels else out[:, : self.out_channels]
+            if y.shape[4] != self.out_channels:
+                return out[:, : self.out_channels]
+            if self._gn_partials is not None:
+                out._sb_gn_partials, self._gn_partials = self._gn_partials, None
+            return out
         xin = xs[0] if len(xs) == 1 else torch.cat([t.to(xs[0].dtype) for t in xs], dim=1)
         sp = self._spatial
         if sp is not None and sp.size > 1 and self.kernel_size[0] > 1:

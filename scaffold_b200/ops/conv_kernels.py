@@ -143,7 +143,8 @@ def conv_same(srcs: Sequence[torch.Tensor], wpack: torch.Tensor, ksize: int,
               dst_channels: Sequence[int], bias: Optional[torch.Tensor] = None,
               force_plain: bool = False, out: Optional[Sequence[torch.Tensor]] = None,
               out_dims: Optional[Sequence[int]] = None, in_off: Sequence[int] = (0, 0, 0), halo=None,
-              slabs: Optional[Sequence[torch.Tensor]] = None, kd_fused: bool = True):
+              slabs: Optional[Sequence[torch.Tensor]] = None, kd_fused: bool = True, gn_groups: int = 0,
+              gn_sink: Optional[list] = None):
     """Stride-1 'same' convolution of the channel concatenation of ``srcs``.
 
     Returns a list of outputs, one per entry of ``dst_channels`` (the output
@@ -151,6 +152,9 @@ def conv_same(srcs: Sequence[torch.Tensor], wpack: torch.Tensor, ksize: int,
     halo'd sources of a sharded volume: output voxel 0 sits at ``in_off`` inside the
     sources (negative offsets read zeros, which is how backward-data grows a halo).
     ``kd_fused=False`` keeps a narrow-output call on the one-tap-per-MMA plane kernel.
+    ``gn_groups`` > 0 asks the kernel to also produce the GroupNorm statistics of its output (groups over
+    the padded output channels); when the call can (kd-fused kernel, one destination) the triple
+    ``(partials, splits, groups)`` is appended to ``gn_sink``, the input of :func:`gn_kernels.gn_finalize`.
     """
     for s in srcs:
         _chk_act(s)
@@ -205,6 +209,15 @@ def conv_same(srcs: Sequence[torch.Tensor], wpack: torch.Tensor, ksize: int,
     if slabs is not None:
         a.slab_out[0], a.slab_out[1] = slabs[0].data_ptr(), slabs[1].data_ptr()
         a.slab_ld = slabs[0].shape[-1]
+    if gn_groups > 0 and gn_sink is not None and len(outs) == 1 and slabs is None:
+        a.gn_groups = int(gn_groups)
+        splits = _lib.lib().sb_conv_gn_splits(C.byref(a))
+        if splits > 0:
+            part = torch.empty(n * splits * gn_groups * 3, dtype=torch.float32, device=srcs[0].device)
+            a.gn_part = part.data_ptr()
+            gn_sink.append((part, splits, int(gn_groups)))
+        else:
+            a.gn_groups = 0
     need = _lib.lib().sb_conv_fwd_workspace(C.byref(a))
     if need > 0:  # kernels that split the reduction keep fp32 partial sums here
         ws = _workspace(srcs[0].device, need)

@@ -98,6 +98,15 @@ def gn_stats(x, w, b, groups, eps, relu, part: Optional[torch.Tensor] = None,
     return fin
 
 
+def gn_finalize(part: torch.Tensor, n: int, groups: int, nsplit: int) -> torch.Tensor:
+    """Collapse ``[N, nsplit, G, 3]`` partial statistics (from ``sb_gn_stats`` or from a convolution's epilogue)
+    into the ``[N*G*3]`` block that ``gn_apply`` merges."""
+    fin = torch.empty(n * groups * 3, dtype=torch.float32, device=part.device)
+    _lib.check(_lib.lib().sb_gn_stats_finalize(part.data_ptr(), fin.data_ptr(), n, groups, nsplit, _lib.stream_ptr()),
+               "sb_gn_stats_finalize")
+    return fin
+
+
 def _set_wait(a: SbGnArgs, wait, device) -> None:
     if wait is not None:
         a.wait_flags, a.wait_epoch = wait[0], wait[1]
@@ -124,8 +133,9 @@ def gn_apply(x, w, b, groups, eps, relu, parts: Sequence[int], shards: int = 1, 
     return y, mean, rstd
 
 
-def gn_forward(x, w, b, groups: int, eps: float = 1e-5, relu: bool = True):
-    part = gn_stats(x, w, b, groups, eps, relu)
+def gn_forward(x, w, b, groups: int, eps: float = 1e-5, relu: bool = True, fin: Optional[torch.Tensor] = None):
+    """``fin``: this tensor's finalised statistics when its producer already computed them (pass 1 is skipped)."""
+    part = fin if fin is not None else gn_stats(x, w, b, groups, eps, relu)
     return gn_apply(x, w, b, groups, eps, relu, [part.data_ptr()])
 
 

@@ -23,12 +23,18 @@ from .layout import from_vm, to_vm, use_cuda_kernels
 
 class _GnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, groups, eps, relu, spatial):
+    def forward(ctx, x, weight, bias, groups, eps, relu, spatial, partials):
         w32, b32 = weight.detach().float().contiguous(), bias.detach().float().contiguous()
+        fin = None
+        if partials is not None:
+            # the producing convolution left (count, mean, M2) partials of this very tensor: no statistics pass
+            part, splits, pg = partials
+            if pg == groups and part.numel() == x.shape[0] * splits * groups * 3:
+                fin = gk.gn_finalize(part, x.shape[0], groups, splits)
         if spatial is None:
-            y, mean, rstd = gk.gn_forward(x, w32, b32, groups, eps, relu)
+            y, mean, rstd = gk.gn_forward(x, w32, b32, groups, eps, relu, fin=fin)
         else:
-            y, mean, rstd = spatial.gn_forward(x, w32, b32, groups, eps, relu)
+            y, mean, rstd = spatial.gn_forward(x, w32, b32, groups, eps, relu, fin=fin)
         ctx.save_for_backward(x, w32, b32, mean, rstd)
         ctx.cfg = (groups, eps, relu, spatial)
         return y
@@ -42,7 +48,7 @@ class _GnFn(torch.autograd.Function):
             dx, dw, db = gk.gn_backward(gy, x, w32, b32, mean, rstd, groups, eps, relu)
         else:
             dx, dw, db = spatial.gn_backward(gy, x, w32, b32, mean, rstd, groups, eps, relu)
-        return dx, dw, db, None, None, None, None
+        return dx, dw, db, None, None, None, None, None
 
 
 class GroupNorm(nn.GroupNorm):
@@ -71,7 +77,8 @@ class GroupNorm(nn.GroupNorm):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         relu = self.activation == "relu"
         if use_cuda_kernels(x) and x.dim() == 5 and self.kernel_supported():
-            y = _GnFn.apply(to_vm(x), self.weight, self.bias, self.num_groups, self.eps, relu, self._spatial)
+            partials = getattr(x, "_sb_gn_partials", None)  # left by the convolution that produced x, if it could
+            y = _GnFn.apply(to_vm(x), self.weight, self.bias, self.num_groups, self.eps, relu, self._spatial, partials)
             return from_vm(y)
         if x.is_cuda and use_cuda_kernels(x) and not self._warned:
             self._warned = True

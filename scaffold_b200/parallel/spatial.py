@@ -131,11 +131,13 @@ class SpatialContext:
         return (y * weight.float().reshape(shape) + bias.float().reshape(shape)).to(x.dtype)
 
     # -- GroupNorm kernels with peer statistics (CUDA path) ---------------------------
-    def gn_forward(self, x, w32, b32, groups, eps, relu):
+    def gn_forward(self, x, w32, b32, groups, eps, relu, fin=None):
+        """``fin``: this shard's finalised statistics when the producing convolution already computed them."""
         from ..ops import gn_kernels as gk
         if self.size == 1 or not self.gn_global:
-            return gk.gn_forward(x, w32, b32, groups, eps, relu)
-        fin = gk.gn_stats(x, w32, b32, groups, eps, relu)
+            return gk.gn_forward(x, w32, b32, groups, eps, relu, fin=fin)
+        if fin is None:
+            fin = gk.gn_stats(x, w32, b32, groups, eps, relu)
         if self.stats_channel is not None:
             parts, wait = self.stats_channel.share(fin)
             return gk.gn_apply(x, w32, b32, groups, eps, relu, parts, shards=self.size, wait=wait)

@@ -164,3 +164,33 @@ def test_kernel_selection_report_lists_every_layer():
     assert by["up_list.0.up"]["fwd"].startswith("igemm")
     text = format_selection(rows, {"halo_exchange_effective": "none"})
     assert "weight-grad" in text and "halo_exchange_effective: none" in text
+
+
+@pytest.mark.parametrize("cin,cout,dims,groups", [(64, 64, (8, 24, 40), 8), (32, 128, (5, 16, 16), 8),
+                                                  (64, 32, (4, 9, 17), 8), (64, 64, (2, 8, 16), 4)],
+                         ids=lambda v: str(v))
+def test_groupnorm_statistics_from_the_convolution_epilogue_match_the_statistics_pass(cin, cout, dims, groups):
+    from scaffold_b200.ops import _lib, conv_kernels as ck, gn_kernels as gk
+    torch.manual_seed(6)
+    d, h, w = dims
+    x = (torch.randn(2, d, h, w, cin, device="cuda") + 0.5).to(torch.bfloat16)
+    wt = torch.randn(cout, cin, 3, 3, 3, device="cuda") * 0.1
+    sink = []
+    (y,) = ck.conv_same([x], ck.pack_weight_fwd(wt), 3, [cout], gn_groups=groups, gn_sink=sink)
+    (y_plain,) = ck.conv_same([x], ck.pack_weight_fwd(wt), 3, [cout])
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert torch.equal(y, y_plain)                      # asking for statistics does not change the output
+    assert len(sink) == 1
+    part, splits, g = sink[0]
+    fin = gk.gn_finalize(part, 2, groups, splits).view(2, groups, 3)
+    wg, bg = torch.ones(cout, device="cuda"), torch.zeros(cout, device="cuda")
+    ref = gk.gn_stats(y, wg, bg, groups, 1e-5, False).view(2, groups, 3)
+    torch.cuda.synchronize()
+    assert torch.equal(fin[..., 0], ref[..., 0])        # element counts
+    assert torch.allclose(fin[..., 1], ref[..., 1], rtol=1e-4, atol=1e-5)
+    assert torch.allclose(fin[..., 2], ref[..., 2], rtol=2e-4)
+    # and through the modules: conv -> GroupNorm picks the partials up
+    ya, _, _ = gk.gn_forward(y, wg, bg, groups, 1e-5, True, fin=fin.reshape(-1))
+    yb, _, _ = gk.gn_forward(y, wg, bg, groups, 1e-5, True)
+    assert (ya.float() - yb.float()).abs().max().item() <= 0.02
