@@ -250,26 +250,65 @@ __global__ void wgrad_reduce_kernel(const ReduceParams p) {
 }
 
 // Same reduction for 3x3x3 weights with the output channel on the workspace's M side (mode 0), through a
-// shared-memory transpose: one block owns (co, 32 input channels): it reads 27 runs of 32 consecutive floats per
-// split (in split order) and writes the 32 x 27 floats that are contiguous in dw[co][ci][tap].
-__global__ void __launch_bounds__(256) wgrad_reduce_t_kernel(const ReduceParams p) {
-  __shared__ float t[27][33];
-  const int co = blockIdx.y, ci0 = blockIdx.x * 32;
+// shared-memory transpose: one block owns (co, CT input channels), CT = 128 when cin allows (else 64 or 32).
+// It reads 27 runs of CT consecutive floats per split as 16-byte vectors, four in flight per thread (summed in
+// split order), and writes the CT x 27 floats that are contiguous in dw[co][ci][tap] as 16-byte vectors.
+constexpr int RT_MAX_CT = 128;
+__global__ void __launch_bounds__(256) wgrad_reduce_t_kernel(const ReduceParams p, const int CT) {
+  __shared__ float t[27][RT_MAX_CT + 1];
+  const int co = blockIdx.y, ci0 = blockIdx.x * CT;
   const size_t slice = (size_t)p.T * p.Mtot * p.Ntot;
-  for (int e = threadIdx.x; e < 27 * 32; e += 256) {
-    const int tap = e >> 5, c = e & 31;
-    const float* src = p.ws + ((size_t)tap * p.Mtot + co) * p.Ntot + ci0 + c;
-    float acc = 0.f;
-    for (int s = 0; s < p.splits; ++s) acc += src[(size_t)s * slice];
-    t[tap][c] = acc;
+  const int v_per_run = CT / 4, nvec = 27 * v_per_run;
+  for (int e0 = threadIdx.x; e0 < nvec; e0 += 4 * 256) {
+    float4 acc[4];
+    int tap[4], c4[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int e = e0 + u * 256;
+      tap[u] = e / v_per_run;
+      c4[u] = (e - tap[u] * v_per_run) * 4;
+      acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int sp = 0; sp < p.splits; ++sp) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (e0 + u * 256 < nvec)
+          v[u] = __ldcs(reinterpret_cast<const float4*>(p.ws + (size_t)sp * slice +
+                                                        ((size_t)tap[u] * p.Mtot + co) * p.Ntot + ci0 + c4[u]));
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (e0 + u * 256 < nvec) {
+        t[tap[u]][c4[u]] = acc[u].x; t[tap[u]][c4[u] + 1] = acc[u].y;
+        t[tap[u]][c4[u] + 2] = acc[u].z; t[tap[u]][c4[u] + 3] = acc[u].w;
+      }
+    }
   }
   __syncthreads();
-  float* dst = p.dw + ((size_t)co * p.cin + ci0) * 27;
-  for (int e = threadIdx.x; e < 27 * 32; e += 256) {
-    const int c = e / 27, tap = e - c * 27;
-    float v = t[tap][c];
-    if (p.accumulate) v += dst[e];
-    dst[e] = v;
+  float* dst = p.dw + ((size_t)co * p.cin + ci0) * 27;  // 16-byte aligned: (co * cin + ci0) is a multiple of 4
+  const int nout4 = CT * 27 / 4;
+  for (int q = threadIdx.x; q < nout4; q += 256) {
+    float o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int e = q * 4 + k;
+      const int c = e / 27, tp = e - c * 27;
+      o[k] = t[tp][c];
+    }
+    float4 v = make_float4(o[0], o[1], o[2], o[3]);
+    float4* d4 = reinterpret_cast<float4*>(dst) + q;
+    if (p.accumulate) {
+      const float4 old = *d4;
+      v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+    }
+    *d4 = v;
   }
 }
 
@@ -482,9 +521,11 @@ static int run_reduce(const SbWgradArgs* a, ReduceParams& r, cudaStream_t stream
   r.total = (long long)r.cout * r.cin * r.taps;
   const int threads = 256;
   const long long blocks = (r.total + threads - 1) / threads;
-  if (r.mode == 0 && r.taps == 27 && r.cin % 32 == 0 && r.cout <= 65535)
-    wgrad_reduce_t_kernel<<<dim3(r.cin / 32, r.cout), threads, 0, stream>>>(r);
-  else
+  if (r.mode == 0 && r.taps == 27 && r.cin % 32 == 0 && r.cout <= 65535 && r.Ntot % 4 == 0 &&
+      (reinterpret_cast<uintptr_t>(r.dw) & 15) == 0 && (reinterpret_cast<uintptr_t>(r.ws) & 15) == 0) {
+    const int ct = r.cin % 128 == 0 ? 128 : (r.cin % 64 == 0 ? 64 : 32);
+    wgrad_reduce_t_kernel<<<dim3(r.cin / ct, r.cout), threads, 0, stream>>>(r, ct);
+  } else
     wgrad_reduce_kernel<<<(unsigned)blocks, threads, 0, stream>>>(r);
   sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;

@@ -242,9 +242,17 @@ __global__ void __launch_bounds__(GN_THREADS) gn_apply_kernel(const GnParams p) 
     }
     *reinterpret_cast<uint4*>(p.y + base + v * p.C) = pack8(f);
   };
+  // four voxels (four 16-byte loads) in flight per thread
   const long long stride = (long long)gridDim.x * vpb;
-  for (long long v = (long long)blockIdx.x * vpb + vl; v < p.S; v += stride)
-    body(__ldg(reinterpret_cast<const uint4*>(p.x + base + v * p.C)), v);
+  long long v = (long long)blockIdx.x * vpb + vl;
+  for (; v + 3 * stride < p.S; v += 4 * stride) {
+    uint4 r[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) r[u] = __ldg(reinterpret_cast<const uint4*>(p.x + base + (v + u * stride) * p.C));
+#pragma unroll
+    for (int u = 0; u < 4; ++u) body(r[u], v + u * stride);
+  }
+  for (; v < p.S; v += stride) body(__ldg(reinterpret_cast<const uint4*>(p.x + base + v * p.C)), v);
 }
 
 // ----------------------------------------------------------------------------

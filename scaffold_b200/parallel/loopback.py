@@ -1,4 +1,5 @@
-"""Two spatial 'ranks' on ONE GPU: channel objects wired to each other's buffers inside one process.
+"""Single-GPU bring-up of the multi-rank protocols: several spatial 'ranks' on ONE GPU, their channel objects
+wired to each other's buffers inside one process (used by the loopback tests and the smoke run).
 
 The fused multi-GPU kernels address their peers through plain device pointers, so on a single device
 rank A's push can land in rank B's arena and vice versa. The producers (push / share kernels, which
@@ -9,8 +10,8 @@ from __future__ import annotations
 
 import torch
 
-from scaffold_b200.parallel.halo import SLOTS, HaloChannel, StatsChannel
-from scaffold_b200.parallel.peer import PeerBuffer
+from .halo import SLOTS, HaloChannel, StatsChannel
+from .peer import PeerBuffer
 
 
 def _buffers(nbytes: int, world: int):
@@ -52,3 +53,26 @@ def stats_pair(world: int = 2):
         c.seq = 0
         chans.append(c)
     return chans
+
+
+def allreduce(tensors, scale: float = 1.0, ctas: int = 8, wait_seconds: float = 0.5) -> None:
+    """Sum ``tensors`` (equal-length fp32 views of PeerBuffer allocations, one per emulated rank) in place with the
+    gradient all-reduce protocol, all ranks in ONE cooperative launch (``sb_grad_allreduce_loopback``)."""
+    import ctypes as C
+
+    from ..ops import _lib
+    world = len(tensors)
+    flags = _buffers(4096, world)
+    _P = C.c_void_p
+    fn = _lib.lib().sb_grad_allreduce_loopback
+    fn.argtypes = [C.POINTER(_P), C.POINTER(_P), C.c_int, C.c_longlong, C.c_longlong, C.c_uint, C.c_float, C.c_int,
+                   C.c_double, _P, _P]
+    fn.restype = C.c_int
+    barr = (_P * world)(*[t.data_ptr() for t in tensors])
+    farr = (_P * world)(*[f.local for f in flags])
+    _lib.check(fn(barr, farr, world, 0, tensors[0].numel(), 1, float(scale), ctas, wait_seconds,
+                  _lib.status_tensor(tensors[0].device).data_ptr(), torch.cuda.current_stream().cuda_stream),
+               "sb_grad_allreduce_loopback")
+    torch.cuda.current_stream().synchronize()
+    for f in flags:
+        f.close()

@@ -1,7 +1,7 @@
 """The fused multi-GPU protocols on ONE GPU (loopback): halo push + convolution, halo-gradient return +
 accumulate, cross-shard GroupNorm statistics, and the gradient all-reduce, each against the unsharded result.
 
-Every consumer runs after both ranks' producers were launched (see ``helpers/loopback.py``); the all-reduce,
+Every consumer runs after both ranks' producers were launched (see ``scaffold_b200/parallel/loopback.py``); the all-reduce,
 whose ranks wait on one another, runs as one cooperative launch over all ranks' buffers.
 """
 import ctypes as C
@@ -10,7 +10,7 @@ import pytest
 import torch
 import torch.nn.functional as F
 
-from helpers.loopback import halo_pair, stats_pair
+from scaffold_b200.parallel.loopback import halo_pair, stats_pair
 
 pytestmark = pytest.mark.gpu
 
