@@ -112,3 +112,35 @@ def test_census_counts_launcher_calls(monkeypatch):
     assert corpus[0]["measured_ms"] == 0.5 and corpus[0]["route"] == "conv_plane3"
     json.dumps(corpus)
     assert ck.conv_same([x], None, 3, [64]) == ["y"]  # launchers restored
+
+
+def test_committed_corpus_fixture_matches_the_analytic_corpus():
+    from scaffold_b200.analysis import corpus
+    from scaffold_b200.analysis.shapes import scaffold_corpus
+    doc = corpus.load()
+    probs = scaffold_corpus(7, 3, 2)
+    assert sum(layer["count"] for layer in doc["layers"]) == len(probs)
+    labels = {p.label for p in probs}
+    assert {layer["label"] for layer in doc["layers"]} == labels
+    for layer in doc["layers"]:
+        for d in ("fwd", "dgrad", "wgrad"):
+            e = layer["directions"][d]
+            assert e["flops"] > 0 and e["roofline_ms"] > 0 and e["route"]
+            if "ms" in e:  # measured rows carry the paired ratio and its interval
+                assert e["ms"] > 0 and e["library_ms"] > 0 and e["ci"][0] <= e["ratio"] <= e["ci"][1]
+    # the fixture answers "which layers matter": the 128^3 layers hold most of the forward time
+    big = sum(layer["count"] * layer["directions"]["fwd"].get("ms", 0) for layer in doc["layers"]
+              if layer["spatial"][0] == 128)
+    assert big > 0.4 * doc["totals"]["fwd"]["ms_per_step"]
+    rebuilt = corpus.build([], 7, 2)
+    assert [layer["label"] for layer in rebuilt["layers"]] == [layer["label"] for layer in doc["layers"]]
+
+
+def test_paired_ratio_statistics():
+    from scaffold_b200.bench.harness import ratio_ci, t95
+    import math
+    g, lo, hi = ratio_ci([math.log(2.0)] * 6)
+    assert abs(g - 2.0) < 1e-12 and abs(lo - 2.0) < 1e-9 and abs(hi - 2.0) < 1e-9
+    g, lo, hi = ratio_ci([math.log(v) for v in (1.9, 2.0, 2.1, 2.0, 1.95, 2.05)])
+    assert lo < g < hi and 1.9 < lo and hi < 2.1
+    assert t95(2) > t95(10) > t95(100) == 1.96 and math.isinf(t95(1))
