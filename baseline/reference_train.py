@@ -76,9 +76,12 @@ def main():
     torch.manual_seed(a.seed)
 
     root = Path(a.dataset_dir)
-    spec = SpatialShardSpec()
-    train_set = FractalDataset(str(root / "volumes" / "training"), str(root / "masks" / "training"), str(root), spec)
-    val_set = FractalDataset(str(root / "volumes" / "validation"), str(root / "masks" / "validation"), str(root), spec)
+    spec = SpatialShardSpec((2, 3, 4), (1, 1, 1), (0, 0, 0))  # one rank holds the whole volume
+    # third argument: the split's pickle of mask values, as the reference trainer passes it (trainer.py:170-181)
+    train_set = FractalDataset(str(root / "volumes" / "training"), str(root / "masks" / "training"),
+                               str(root / "train_unique_mask_vals"), spec)
+    val_set = FractalDataset(str(root / "volumes" / "validation"), str(root / "masks" / "validation"),
+                             str(root / "val_unique_mask_vals"), spec)
     n_classes = a.n_categories + 1
     model = UNet(3, n_classes, trilinear=False, layers=a.scale - a.bottleneck_dim, group_norm_groups=8)
     model = model.to(device=device, memory_format=torch.channels_last_3d)

@@ -135,7 +135,7 @@ def find_reusable(id_dir: Path, require_commit: Optional[str] = None) -> Optiona
             continue
         if info.get("dataset_format_version") != DATASET_FORMAT_VERSION:
             continue
-        if require_commit and info.get("commit") != require_commit:
+        if require_commit and info.get("code_commit", info.get("commit")) != require_commit:
             continue
         best = d
     return best
@@ -179,9 +179,12 @@ def get_dataset(config, require_commit: bool = False, log=None) -> Path:
             raise interrupt
 
     def publish():
-        meta = dict(volume_config(config))
-        meta.update({"config_id": cid, "commit": commit, "created": datetime.datetime.now().isoformat(),
-                     "vol_size": int(config.vol_size), "point_num": int(config.point_num)})
+        # the reference's schema (ScaFFold/datagen/get_dataset.py:527-535): the keys that define the dataset live
+        # under `config_subset`, so either implementation's loader reads the other's datasets
+        meta = {"config_id": cid, "dataset_format_version": DATASET_FORMAT_VERSION,
+                "config_subset": dict(volume_config(config)), "include_keys": list(INCLUDE_KEYS),
+                "code_commit": commit, "created_at": time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime()),
+                "vol_size": int(config.vol_size), "point_num": int(config.point_num)}
         with open(staging / META_FILENAME, "w") as f:
             yaml.safe_dump(meta, f, sort_keys=True)
             f.flush()

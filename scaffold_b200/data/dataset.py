@@ -110,7 +110,11 @@ class FractalDataset(Dataset):
 
     # -- index ----------------------------------------------------------------
     def _check_physical_layout(self) -> None:
-        disk = canonical_sharding(self.meta.get("dc_num_shards", [1, 1, 1]), self.meta.get("dc_shard_dims", [2, 3, 4]))
+        layout = self.meta.get("config_subset") or self.meta  # reference schema first, flat keys of older datasets
+        if layout.get("dc_num_shards") is None or layout.get("dc_shard_dims") is None:
+            raise RuntimeError("Physical dataset is missing shard metadata. Expected config_subset.dc_num_shards / "
+                               "config_subset.dc_shard_dims in meta.yaml.")
+        disk = canonical_sharding(layout["dc_num_shards"], layout["dc_shard_dims"])
         want = canonical_sharding(self.spec.num_shards, self.spec.shard_dims)
         if disk != want:
             raise ValueError(

@@ -127,6 +127,39 @@ def test_sharded_dataset_files_tile_the_whole_volume(tmp_path):
         FractalDataset(sharded / "volumes" / "training", sharded / "masks" / "training", str(sharded))
 
 
+def test_reference_dataset_class_reads_a_generated_sharded_dataset(tmp_path):
+    """Format interchange: the reference's own ``FractalDataset`` (when its package is installed under
+    ``baseline/_ref``) opens a dataset this framework wrote, meta.yaml included, and returns the same tensors."""
+    import sys
+    from pathlib import Path
+    ref = Path(__file__).resolve().parents[1] / "baseline" / "_ref"
+    if not (ref / "ScaFFold").exists():
+        pytest.skip("the reference package is not installed under baseline/_ref")
+    cfg = tiny_config(tmp_path, dc_num_shards=[1, 1, 2])
+    category_search.main(cfg)
+    instances.main(cfg)
+    path = cache.get_dataset(cfg)
+    import yaml
+    meta = yaml.safe_load((path / "meta.yaml").read_text())
+    assert meta["config_subset"]["dc_num_shards"] and meta["dataset_format_version"] == 5 and meta["code_commit"]
+    sys.path.insert(0, str(ref))
+    try:
+        from ScaFFold.utils.data_loading import FractalDataset as RefDataset, SpatialShardSpec as RefSpec
+    except Exception as exc:  # a dependency of the reference is missing here
+        pytest.skip(f"reference data loader does not import: {exc}")
+    finally:
+        sys.path.remove(str(ref))
+    import torch
+    for i in range(2):
+        theirs = RefDataset(str(path / "volumes" / "training"), str(path / "masks" / "training"),
+                            str(path / "train_unique_mask_vals"), RefSpec((2, 3, 4), (1, 1, 2), (0, 0, i)))
+        ours = FractalDataset(path / "volumes" / "training", path / "masks" / "training", str(path),
+                              SpatialShardSpec((1, 1, 2), (2, 3, 4), (0, 0, i)))
+        assert len(theirs) == len(ours)
+        assert torch.equal(theirs[0]["image"], ours[0]["image"])
+        assert torch.equal(theirs[0]["mask"].long(), ours[0]["mask"].long())
+
+
 def test_cache_key_ignores_irrelevant_keys_and_canonicalises_shard_order(tmp_path):
     a = tiny_config(tmp_path)
     b = tiny_config(tmp_path, local_batch_size=4, training_seed=7)
