@@ -100,7 +100,7 @@ def main():
     def loss_of(preds, labels):
         with torch.autocast("cuda", enabled=False):
             log_probs = F.log_softmax(preds.float(), dim=1)
-            ce = compute_sharded_cross_entropy_loss(preds, labels, weights, [1, 1, 1], "cuda", None, log_probs=log_probs)
+            ce = compute_sharded_cross_entropy_loss(preds, labels, None, [1, 1, 1], "cuda", weights, log_probs=log_probs)
             dice = compute_sharded_dice(log_probs.exp(), labels_to_onehot(labels, n_classes), None)
         return ce + (1.0 - dice[:, 1:].mean())
 
