@@ -219,8 +219,15 @@ struct ReduceParams {
   int splits, T, Mtot, Ntot;
   int mode, cout, cin, taps;
   int accumulate;
+  int tap_swap;  // 3x3x3: destination tap order differs from the workspace's (0 none, 1 kd <-> kh, 2 kd <-> kw)
   long long total;
 };
+
+__device__ __forceinline__ int wg_swap_tap(int tap, int mode) {
+  if (mode == 0) return tap;
+  const int kd = tap / 9, kh = (tap / 3) % 3, kw = tap % 3;
+  return mode == 1 ? (kh * 9 + kd * 3 + kw) : (kw * 9 + kh * 3 + kd);
+}
 
 __global__ void wgrad_reduce_kernel(const ReduceParams p) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -237,6 +244,7 @@ __global__ void wgrad_reduce_kernel(const ReduceParams p) {
     n = kw * p.cout + co;
   } else {
     tap = (int)(idx % p.taps);
+    if (p.taps == 27) tap = wg_swap_tap(tap, p.tap_swap);  // idx walks the parameter's order; ws holds the kernels'
     const int ci = (int)((idx / p.taps) % p.cin);
     const int co = (int)(idx / ((long long)p.taps * p.cin));
     if (p.mode == 0) { m = co; n = ci; } else { m = ci; n = co; }
@@ -299,7 +307,7 @@ __global__ void __launch_bounds__(256) wgrad_reduce_t_kernel(const ReduceParams 
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const int e = q * 4 + k;
-      const int c = e / 27, tp = e - c * 27;
+      const int c = e / 27, tp = wg_swap_tap(e - c * 27, p.tap_swap);
       o[k] = t[tp][c];
     }
     float4 v = make_float4(o[0], o[1], o[2], o[3]);
@@ -518,6 +526,8 @@ static int run_reduce(const SbWgradArgs* a, ReduceParams& r, cudaStream_t stream
   r.cout = a->dw_cout;
   r.cin = a->dw_cin;
   r.taps = a->ksize == 3 ? 27 : (a->ksize == 2 ? 8 : 1);
+  r.tap_swap = a->ksize == 3 ? a->tap_swap : 0;
+  if (r.tap_swap < 0 || r.tap_swap > 2) return SB_ERR_SHAPE;
   r.total = (long long)r.cout * r.cin * r.taps;
   const int threads = 256;
   const long long blocks = (r.total + threads - 1) / threads;

@@ -76,6 +76,9 @@ typedef struct {
   void* fwd_kd;
   void* dgrad;
   void* dgrad_kd;
+  // Volume processed with two spatial axes exchanged (a split along H or W runs as a split along depth): the
+  // kernels then need the weight with the same two tap axes exchanged. 0 none, 1 kd <-> kh, 2 kd <-> kw.
+  int tap_swap;
 } SbPackArgs;
 
 // One entry of the whole-model packing table (sb_pack_conv3_batch): tile0 / tiles_x are filled by sb_pack_conv3_plan.
@@ -122,6 +125,9 @@ typedef struct {
   int xoff_d, xoff_h, xoff_w;
   // depth halo of x kept as separate slabs [N,1,H,W,x_c[s]] (see SbConvArgs.halo_land); null = zeros
   const void* xhalo[2][2];
+  // same exchange as SbPackArgs.tap_swap (3x3x3 only): the gradient is computed in the kernels' tap order and
+  // stored into dw in the parameter's own order
+  int tap_swap;
 } SbWgradArgs;
 
 // GroupNorm (+ReLU), channels-last bf16. `parts` lists the partial-statistics

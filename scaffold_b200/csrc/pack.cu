@@ -26,6 +26,13 @@ __device__ __forceinline__ int kd_pos(int p) {  // (kd,kh,kw) index -> (kh,kw,2-
   return r * 3 + (2 - kd);
 }
 
+// tap (kd,kh,kw) with two axes exchanged: 1 kd <-> kh, 2 kd <-> kw (an involution)
+__device__ __forceinline__ int swap_tap(int tap, int mode) {
+  if (mode == 0) return tap;
+  const int kd = tap / 9, kh = (tap / 3) % 3, kw = tap % 3;
+  return mode == 1 ? (kh * 9 + kd * 3 + kw) : (kw * 9 + kh * 3 + kd);
+}
+
 // Tile in shared memory as [tap][co][ci], rows padded to 34 elements so that the transposed read of the
 // backward-data layouts spreads over the banks. Global reads are contiguous runs of 32 x 27 floats; global
 // writes are 16-byte pieces of 64-byte rows.
@@ -63,7 +70,7 @@ __device__ __forceinline__ void pack_tile(const SbPackArgs& a, const int bx, con
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int j = jj[u] + q;
-          const int ci = j / 27, tap = j - ci * 27;
+          const int ci = j / 27, tap = swap_tap(j - ci * 27, a.tap_swap);
           tile[tap * PK_PLANE + rr[u] * PK_LD + ci] = __float2bfloat16(e[q]);
         }
       }
@@ -71,7 +78,7 @@ __device__ __forceinline__ void pack_tile(const SbPackArgs& a, const int bx, con
   } else {
     for (int i = threadIdx.x; i < PK_T * PK_T * 27; i += blockDim.x) {
       const int r = i / (PK_T * 27), j = i - r * (PK_T * 27);
-      const int ci = j / 27, tap = j - ci * 27;
+      const int ci = j / 27, tap = swap_tap(j - ci * 27, a.tap_swap);
       float v = 0.f;
       if (r < nco && j < run) v = a.w[((long long)(co0 + r) * a.cin + ci0) * 27 + j];
       tile[tap * PK_PLANE + r * PK_LD + ci] = __float2bfloat16(v);
@@ -182,7 +189,7 @@ static int pack_configure(int smem) {
 
 static bool pack_args_ok(const SbPackArgs* a) {
   return !(a->cout <= 0 || a->cin <= 0 || a->real0 > a->pad0 || a->cin - a->real0 + a->pad0 > a->cin_pad ||
-           a->cout > a->cout_pad);
+           a->cout > a->cout_pad || a->tap_swap < 0 || a->tap_swap > 2);
 }
 
 // Fills tile0 / tiles_x of `njobs` host-side jobs (validating each) and returns the total tile count, or -1.

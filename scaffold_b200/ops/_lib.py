@@ -66,6 +66,7 @@ class SbPackArgs(C.Structure):
         ("cout", C.c_int), ("cin", C.c_int), ("real0", C.c_int), ("pad0", C.c_int),
         ("cin_pad", C.c_int), ("cout_pad", C.c_int),
         ("fwd", C.c_void_p), ("fwd_kd", C.c_void_p), ("dgrad", C.c_void_p), ("dgrad_kd", C.c_void_p),
+        ("tap_swap", C.c_int),
     ]
 
 
@@ -106,6 +107,7 @@ class SbWgradArgs(C.Structure):
         ("xin_d", C.c_int), ("xin_h", C.c_int), ("xin_w", C.c_int),
         ("xoff_d", C.c_int), ("xoff_h", C.c_int), ("xoff_w", C.c_int),
         ("xhalo", (C.c_void_p * 2) * 2),
+        ("tap_swap", C.c_int),
     ]
 
 

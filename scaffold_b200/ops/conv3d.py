@@ -59,13 +59,13 @@ def repack_all() -> int:
             members.append((cache, w, sig, cache._real[sig], bufs))
     if not members:
         return 0
-    key = tuple((id(c), w.data_ptr(), sig, tuple((n, b.data_ptr()) for n, b in sorted(bufs.items())))
+    key = tuple((id(c), w.data_ptr(), sig, c._tap_swap, tuple((n, b.data_ptr()) for n, b in sorted(bufs.items())))
                 for c, w, sig, _, bufs in members)
     plan = _PACK_PLAN
     if plan["key"] != key:
         jobs = (_lib.SbPackJob * len(members))()
         for j, (_, w, sig, real_c, bufs) in enumerate(members):
-            ck.fill_pack_args(jobs[j].a, w, sig, real_c, bufs)
+            ck.fill_pack_args(jobs[j].a, w, sig, real_c, bufs, cache._tap_swap)
         total = _lib.lib().sb_pack_conv3_plan(jobs, len(members))
         if total < 1:
             raise _lib.NativeError("sb_pack_conv3_plan refused the packing table")
@@ -86,26 +86,29 @@ class _PackCache:
         self._key = None
         self._w_ref = None    # the parameter these copies belong to (set on first use)
         self._real = {}       # source signature -> real channels per source
+        self._tap_swap = 0    # tap-axis exchange the packs were made with (sharded runs, see Conv3d._tap_swap)
         self._vals = {}
         self._asked = set()   # (layout name, source signature) ever requested: packed together
         self._fresh = set()   # of those, the ones that hold the current weights
         self._bufs = {}       # persistent operand buffers (padding positions stay zero)
 
-    def _sync(self, w: torch.Tensor):
-        # strides: the same parameter may be read through a tap-transposed view (sharded runs) or directly
-        key = (w.data_ptr(), w._version, w.device, weights_epoch(), tuple(w.stride()))
+    def _sync(self, w: torch.Tensor, tap_swap: Optional[int] = None):
+        # strides / tap exchange: the same parameter may be read tap-transposed (sharded runs) or directly
+        if tap_swap is not None:
+            self._tap_swap = int(tap_swap)
+        key = (w.data_ptr(), w._version, w.device, weights_epoch(), tuple(w.stride()), self._tap_swap)
         if key != self._key:
             self._key = key
             self._vals = {}
             self._fresh = set()
 
-    def conv3(self, w: torch.Tensor, src_c, real_c, kind: str, kd: bool) -> "ck.Packed":
+    def conv3(self, w: torch.Tensor, src_c, real_c, kind: str, kd: bool, tap_swap: int = 0) -> "ck.Packed":
         """Operand copy of a 3x3x3 weight for ``kind`` in ('fwd', 'dgrad'), taps kd-ordered if ``kd``.
 
         Every layout this module has ever asked for with the same sources is refreshed by the same
         kernel launch, so a step packs each weight once.
         """
-        self._sync(w)
+        self._sync(w, tap_swap)
         sig = tuple(src_c)
         name = kind + ("_kd" if kd else "")
         if (name, sig) not in self._fresh:
@@ -124,7 +127,7 @@ class _PackCache:
                     shape = (27, co_pad, k_pad) if nm.startswith("fwd") else (27, k_pad, co_pad)
                     buf = self._bufs[bkey] = torch.zeros(shape, dtype=torch.bfloat16, device=w.device)
                 want[nm] = buf
-            ck.pack_conv3(w, sig, real_c, want)
+            ck.pack_conv3(w, sig, real_c, want, tap_swap)
             self._fresh.update(group)
         buf = self._bufs[(name, sig, w.device)]
         return ck.Packed(None if kd else buf, buf if kd else None)
@@ -166,13 +169,14 @@ class _ConvSameFn(torch.autograd.Function):
         out_dims = tuple(d - 2 * o for d, o in zip(in_dims, in_off))
         src_c = [x.shape[4] for x in xs]
         real_c = mod._real_in_channels(src_c)
+        ts = mod._tap_swap() if ks == 3 else 0
         if fwd_xs is not None:
             f_src = [x.shape[4] for x in fwd_xs]
             wf = mod._cache.conv3(weight, f_src, real_c, "fwd",
-                                  ck.kd_eligible(ck.pad_channels(weight.shape[0]), sum(f_src), out_dims, f_src[0]))
+                                  ck.kd_eligible(ck.pad_channels(weight.shape[0]), sum(f_src), out_dims, f_src[0]), ts)
         elif ks == 3:
             kd = ck.kd_eligible(ck.pad_channels(weight.shape[0]), sum(src_c), out_dims, src_c[0])
-            wf = mod._cache.conv3(weight, src_c, real_c, "fwd", kd)
+            wf = mod._cache.conv3(weight, src_c, real_c, "fwd", kd, ts)
         else:
             wf = mod._cache.get(weight, f"fwd{src_c}",
                                 lambda w: ck.pack_weight_fwd(_pad_in_channels(w, src_c, real_c)))
@@ -189,6 +193,7 @@ class _ConvSameFn(torch.autograd.Function):
         ctx.wparam = weight  # the caller's tensor itself: backward may add into its flat-buffer .grad
         ctx.in_off, ctx.in_dims = in_off, in_dims
         ctx.src_c, ctx.real_c = src_c, real_c
+        ctx.tap_swap = ts
         ctx.has_bias = bias is not None
         ctx.save_for_backward(weight, *xs)
         return y
@@ -206,7 +211,7 @@ class _ConvSameFn(torch.autograd.Function):
             if ks == 3:
                 # rows = input channels of the layer, K = gy's channels (Cout padded to a multiple of 16)
                 kd = ck.kd_eligible(sum(src_c), gy.shape[4], ctx.in_dims)
-                wd = mod._cache.conv3(weight, src_c, real_c, "dgrad", kd)
+                wd = mod._cache.conv3(weight, src_c, real_c, "dgrad", kd, ctx.tap_swap)
             else:
                 wd = mod._cache.get(weight, f"dgrad{src_c}",
                                     lambda w: ck.pack_weight_dgrad(_pad_in_channels(w, src_c, real_c)))
@@ -220,16 +225,16 @@ class _ConvSameFn(torch.autograd.Function):
             direct = direct_grad_target(ctx.wparam) if list(src_c) == list(real_c) else None
             if direct is not None:
                 # the ordered split-K reduce adds straight into the parameter's slice of the flat gradient buffer
-                ck.conv_wgrad(gy, list(xs), ks, direct, accumulate=True, x_off=ctx.in_off)
+                ck.conv_wgrad(gy, list(xs), ks, direct, accumulate=True, x_off=ctx.in_off, tap_swap=ctx.tap_swap)
                 notify_grad_written(ctx.wparam)
             elif list(src_c) == list(real_c):
                 gw = torch.empty(weight.shape, dtype=torch.float32, device=weight.device)  # contiguous whatever the parameter layout
-                ck.conv_wgrad(gy, list(xs), ks, gw, x_off=ctx.in_off)
+                ck.conv_wgrad(gy, list(xs), ks, gw, x_off=ctx.in_off, tap_swap=ctx.tap_swap)
             else:
                 # channel-padded sources (the 3-channel stem): gradient over padded Cin, then slice
                 gw = None
                 gwp = torch.empty((weight.shape[0], sum(src_c), ks, ks, ks), dtype=torch.float32, device=gy.device)
-                ck.conv_wgrad(gy, list(xs), ks, gwp, x_off=ctx.in_off)
+                ck.conv_wgrad(gy, list(xs), ks, gwp, x_off=ctx.in_off, tap_swap=ctx.tap_swap)
                 parts, o = [], 0
                 for sc, rc in zip(src_c, real_c):
                     parts.append(gwp[:, o:o + rc])
@@ -247,7 +252,8 @@ class _ConvHaloFn(torch.autograd.Function):
     def forward(ctx, weight, bias, mod, chan, *xs):
         src_c = [x.shape[4] for x in xs]
         kd = ck.kd_eligible(ck.pad_channels(weight.shape[0]), sum(src_c), xs[0].shape[1:4], src_c[0])
-        wf = mod._cache.conv3(weight, src_c, src_c, "fwd", kd)
+        ts = mod._tap_swap()
+        wf = mod._cache.conv3(weight, src_c, src_c, "fwd", kd, ts)
         cout_pad = wf.shape[1]
         landing = chan.exchange([x[:, 0] for x in xs], [x[:, -1] for x in xs])
         sink = []
@@ -256,7 +262,7 @@ class _ConvHaloFn(torch.autograd.Function):
         mod._gn_partials = sink[0] if sink else None
         ctx.halo_saved = landing.clone()  # the arena slot is recycled; backward needs the planes again
         ctx.mod, ctx.chan, ctx.src_c = mod, chan, src_c
-        ctx.wparam = weight
+        ctx.wparam, ctx.tap_swap = weight, ts
         ctx.save_for_backward(weight, *xs)
         return y
 
@@ -269,7 +275,7 @@ class _ConvHaloFn(torch.autograd.Function):
         gxs: List[Optional[torch.Tensor]] = [None] * len(xs)
         if any(ctx.needs_input_grad[4 + i] for i in range(len(xs))):
             kd = ck.kd_eligible(sum(src_c), gy.shape[4], (d + 2, h, w))
-            wd = mod._cache.conv3(weight, src_c, src_c, "dgrad", kd)
+            wd = mod._cache.conv3(weight, src_c, src_c, "dgrad", kd, ctx.tap_swap)
             ctot = sum(src_c)
             slabs = [torch.empty((n, 1, h, w, ctot), dtype=torch.bfloat16, device=gy.device) for _ in range(2)]
             outs = ck.conv_same([gy], wd, 3, src_c, out_dims=(d + 2, h, w), in_off=(-1, 0, 0), slabs=slabs,
@@ -285,11 +291,11 @@ class _ConvHaloFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             direct = direct_grad_target(ctx.wparam)
             if direct is not None:
-                ck.conv_wgrad(gy, list(xs), 3, direct, accumulate=True, x_halo=ctx.halo_saved)
+                ck.conv_wgrad(gy, list(xs), 3, direct, accumulate=True, x_halo=ctx.halo_saved, tap_swap=ctx.tap_swap)
                 notify_grad_written(ctx.wparam)
             else:
                 gw = torch.empty(weight.shape, dtype=torch.float32, device=weight.device)  # contiguous whatever the parameter layout
-                ck.conv_wgrad(gy, list(xs), 3, gw, x_halo=ctx.halo_saved)
+                ck.conv_wgrad(gy, list(xs), 3, gw, x_halo=ctx.halo_saved, tap_swap=ctx.tap_swap)
         return (gw, None, None, None, *gxs)
 
 
@@ -308,9 +314,16 @@ class Conv3d(nn.Conv3d):
         self._spatial = ctx
 
     def _w(self) -> torch.Tensor:
-        """The weight as the kernels' axes see it: tap axes exchanged like the volume's (``lead_swap``), a view."""
+        """The weight as the kernels' axes see it: tap axes exchanged like the volume's (``lead_swap``), a view
+        (ATen path; the kernel path passes the parameter itself plus ``_tap_swap`` so that the packing and the
+        weight-gradient kernels do the exchange and the flat-buffer fast paths stay on)."""
         k = getattr(self._spatial, "lead_swap", None)
         return self.weight if k is None else self.weight.transpose(2, k)
+
+    def _tap_swap(self) -> int:
+        """0, or which tap axis the kernels exchange with kd: 1 = kh (volume split along H), 2 = kw (along W)."""
+        k = getattr(self._spatial, "lead_swap", None)
+        return 0 if k is None else k - 2
 
     def _real_in_channels(self, src_c: Sequence[int]) -> List[int]:
         """Real (unpadded) channel count of each source; only a single source may be padded."""
@@ -357,7 +370,7 @@ class Conv3d(nn.Conv3d):
             real = self._real_in_channels([v.shape[4] for v in vms])
             if h >= 8 and w >= 16 and d >= 2 and self.bias is None and real == [v.shape[4] for v in vms] \
                     and self.out_channels % 16 == 0:
-                return _ConvHaloFn.apply(self._w(), self.bias, self, sp.halo_channel, *vms)
+                return _ConvHaloFn.apply(self.weight, self.bias, self, sp.halo_channel, *vms)
         if sp is not None and sp.size > 1 and self.kernel_size[0] > 1:
             halo = self.kernel_size[0] // 2
             xs = [sp.halo_pad(t, halo) for t in xs]
@@ -369,7 +382,7 @@ class Conv3d(nn.Conv3d):
             # few input channels (the stem): the forward pass reads a copy padded to 32 channels so that it runs
             # the kd-fused kernel; the weight gradient keeps the 16-channel copy
             fwd_vms = (to_vm(xs[0], pad16=True, pad_to=32),)
-        return _ConvSameFn.apply(self._w(), self.bias, self, off, fwd_vms, *vms)
+        return _ConvSameFn.apply(self.weight, self.bias, self, off, fwd_vms, *vms)
 
     def forward_padded(self, x) -> torch.Tensor:
         """CUDA path only: voxel-major output with the channel axis padded to a multiple of 16."""

@@ -76,7 +76,7 @@ def kd_eligible(rows: int, k: int, out_dims: Sequence[int], first_src: Optional[
             and first % 32 == 0)
 
 
-def pack_conv3(w: torch.Tensor, src_c: Sequence[int], real_c: Sequence[int], want: dict) -> None:
+def pack_conv3(w: torch.Tensor, src_c: Sequence[int], real_c: Sequence[int], want: dict, tap_swap: int = 0) -> None:
     """Fill the requested operand layouts of a 3x3x3 weight ``[Cout, Cin, 3,3,3]`` (fp32) in one kernel.
 
     ``want`` maps 'fwd' / 'fwd_kd' / 'dgrad' / 'dgrad_kd' to zero-initialised bf16 buffers
@@ -86,12 +86,15 @@ def pack_conv3(w: torch.Tensor, src_c: Sequence[int], real_c: Sequence[int], wan
     """
     a = _lib.SbPackArgs()
     wc = w.detach().contiguous().float()
-    fill_pack_args(a, wc, src_c, real_c, want)
+    fill_pack_args(a, wc, src_c, real_c, want, tap_swap)
     _lib.check(_lib.lib().sb_pack_conv3(C.byref(a), _lib.stream_ptr()), "sb_pack_conv3")
 
 
-def fill_pack_args(a, wc: torch.Tensor, src_c: Sequence[int], real_c: Sequence[int], want: dict) -> None:
-    """Describe one packing job: ``wc`` is the contiguous fp32 weight, ``want`` the layouts to write."""
+def fill_pack_args(a, wc: torch.Tensor, src_c: Sequence[int], real_c: Sequence[int], want: dict,
+                   tap_swap: int = 0) -> None:
+    """Describe one packing job: ``wc`` is the contiguous fp32 weight, ``want`` the layouts to write;
+    ``tap_swap`` 1 / 2 packs the weight with the (kd, kh) / (kd, kw) tap axes exchanged."""
+    a.tap_swap = int(tap_swap)
     co, ci = wc.shape[:2]
     a.w = wc.data_ptr()
     a.cout, a.cin = co, ci
@@ -274,7 +277,7 @@ def _workspace(device, elems: int) -> torch.Tensor:
 
 def conv_wgrad(gy: torch.Tensor, xs: Sequence[torch.Tensor], ksize: int, dw: torch.Tensor,
                accumulate: bool = False, splits: int = 0, x_off: Sequence[int] = (0, 0, 0),
-               x_halo=None) -> torch.Tensor:
+               x_halo=None, tap_swap: int = 0) -> torch.Tensor:
     """Weight gradient into ``dw`` (fp32, parameter layout).
 
     ksize 1/3: ``dw`` is [Cout, Cin, k,k,k]; ``gy`` and ``xs`` share the voxel grid.
@@ -303,6 +306,7 @@ def conv_wgrad(gy: torch.Tensor, xs: Sequence[torch.Tensor], ksize: int, dw: tor
                 a.xhalo[si][f] = pair[f].data_ptr() if pair[f] is not None else None
     a.ksize = ksize
     a.splits = splits
+    a.tap_swap = int(tap_swap) if ksize == 3 else 0
     a.accumulate = 1 if accumulate else 0
     if not (dw.dtype == torch.float32 and dw.is_contiguous()):
         raise ValueError("dw must be contiguous fp32")
@@ -315,7 +319,8 @@ def conv_wgrad(gy: torch.Tensor, xs: Sequence[torch.Tensor], ksize: int, dw: tor
     if need < 0:
         if len(xs) == 2 and x_halo is None:
             # two narrow sources (below the kernels' 64-channel source tiles): reduce over their concatenation
-            return conv_wgrad(gy, [torch.cat(list(xs), dim=4)], ksize, dw, accumulate, splits, x_off)
+            return conv_wgrad(gy, [torch.cat(list(xs), dim=4)], ksize, dw, accumulate, splits, x_off,
+                              tap_swap=tap_swap)
         raise _lib.NativeError(f"sb_conv_wgrad: unsupported shape gy={tuple(gy.shape)} xs={[tuple(x.shape) for x in xs]}")
     ws = _workspace(gy.device, need)
     a.workspace, a.workspace_elems = ws.data_ptr(), ws.numel()

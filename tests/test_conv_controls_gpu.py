@@ -194,3 +194,35 @@ def test_groupnorm_statistics_from_the_convolution_epilogue_match_the_statistics
     ya, _, _ = gk.gn_forward(y, wg, bg, groups, 1e-5, True, fin=fin.reshape(-1))
     yb, _, _ = gk.gn_forward(y, wg, bg, groups, 1e-5, True)
     assert (ya.float() - yb.float()).abs().max().item() <= 0.02
+
+
+@pytest.mark.parametrize("swap,axis", [(1, 3), (2, 4)], ids=["kd_kh", "kd_kw"])
+def test_tap_exchange_in_the_pack_and_weight_gradient_kernels_equals_a_transposed_weight(swap, axis):
+    """A volume split along H or W is processed with that axis exchanged with depth; the kernels then pack the
+    weight, and store its gradient, with the matching tap axes exchanged. Both must equal doing the exchange on
+    the tensors with torch."""
+    _lib, ck = _ck()
+    g = torch.Generator(device="cuda").manual_seed(12)
+    cin, cout = 64, 32
+    wt = tri((cout, cin, 3, 3, 3), g, density=0.6)
+    want = {n: torch.zeros((27, cout, cin) if n.startswith("fwd") else (27, cin, cout), dtype=torch.bfloat16,
+                           device="cuda") for n in ("fwd", "fwd_kd", "dgrad", "dgrad_kd")}
+    ck.pack_conv3(wt, [cin], [cin], want, tap_swap=swap)
+    wt_t = wt.transpose(2, axis).contiguous()
+    ref_f, ref_d = ck.pack_weight_fwd(wt_t), ck.pack_weight_dgrad(wt_t)
+    torch.cuda.synchronize()
+    assert torch.equal(want["fwd"], ref_f) and torch.equal(want["dgrad"], ref_d)
+    assert torch.equal(want["fwd_kd"], ck.kd_order(ref_f)) and torch.equal(want["dgrad_kd"], ck.kd_order(ref_d))
+    # weight gradient: computed in the kernels' tap order, stored in the parameter's
+    x = tri((1, cin, 4, 16, 32), g, density=0.5)
+    gy = tri((1, cout, 4, 16, 32), g, density=0.5)
+    plain = torch.empty_like(wt)
+    swapped = torch.full_like(wt, float("nan"))
+    ck.conv_wgrad(ndhwc(gy), [ndhwc(x)], 3, plain)
+    ck.conv_wgrad(ndhwc(gy), [ndhwc(x)], 3, swapped, tap_swap=swap)
+    ck.conv_wgrad(ndhwc(gy), [ndhwc(x)], 3, swapped, tap_swap=swap, accumulate=True)
+    generic = torch.empty_like(wt)
+    ck.conv_wgrad(ndhwc(gy), [ndhwc(x)], 3, generic, tap_swap=swap, splits=-1)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert torch.equal(swapped, 2 * plain.transpose(2, axis)) and torch.equal(generic, plain.transpose(2, axis))
