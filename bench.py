@@ -37,7 +37,8 @@ def parse_args():
     ap.add_argument("--bottleneck-dim", type=int, default=3)
     ap.add_argument("--dc-num-shards", type=int, nargs=3, default=[1, 1, 1])
     ap.add_argument("--grad-allreduce", default="fused", choices=["fused", "nccl"])
-    ap.add_argument("--grad-overlap", action="store_true", help="reduce gradient buckets on a side stream during backward")
+    ap.add_argument("--grad-overlap", action=argparse.BooleanOptionalAction, default=True,
+                    help="reduce gradient buckets on a side stream during backward (--no-grad-overlap: one call after it)")
     ap.add_argument("--halo-exchange", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--gn-stats", default="global", choices=["global", "per_shard"])
     return ap.parse_args()

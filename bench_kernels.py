@@ -43,9 +43,9 @@ def peaks():
     return 1590.0, 6650.0, "fallback"
 
 
-def build(op, cin, cout, size, batch, ref=True, kd_fused=True) -> cases.Case:
+def build(op, cin, cout, size, batch, ref=True, kd_fused=True, gn_groups=0) -> cases.Case:
     if op in ("conv_fwd", "conv_dgrad", "conv_wgrad"):
-        return cases.conv_case(op, cin, cout, size, batch, kd_fused, ref)
+        return cases.conv_case(op, cin, cout, size, batch, kd_fused, ref, gn_groups if op == "conv_fwd" else 0)
     if op in ("convT_fwd", "convT_dgrad"):
         return cases.convT_case(op, cin, cout, size, batch, ref)
     if op in ("gn_fwd", "gn_bwd"):
@@ -61,9 +61,9 @@ def build(op, cin, cout, size, batch, ref=True, kd_fused=True) -> cases.Case:
     raise SystemExit(f"unknown op {op}")
 
 
-def run(op, cin, cout, size, batch, ref=True, kd_fused=True, clocks=None, budget_s=12.0):
+def run(op, cin, cout, size, batch, ref=True, kd_fused=True, clocks=None, budget_s=12.0, gn_groups=0):
     tf_peak, bw_peak, which = peaks()
-    case = build(op, cin, cout, size, batch, ref, kd_fused)
+    case = build(op, cin, cout, size, batch, ref, kd_fused, gn_groups)
     res = paired_ratio(case.ours, case.library if ref else None, clocks=clocks, budget_s=budget_s)
     _lib.check_status()
     ms = res.a.median_ms
@@ -165,6 +165,9 @@ def main():
     ap.add_argument("--budget", type=float, default=12.0, help="seconds per point before the pairing loop gives up")
     ap.add_argument("--no-ref", action="store_true")
     ap.add_argument("--no-kd-fused", action="store_true", help="narrow-output 3x3x3 convs on the one-tap-per-MMA kernel")
+    ap.add_argument("--gn-groups", type=int, default=0, help="conv_fwd: also produce GroupNorm statistics in the epilogue")
+    ap.add_argument("--quick", action="store_true",
+                    help="a handful of calls of our kernel only, no pairing loop (the form to run under a profiler)")
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--grid", action="store_true")
     ap.add_argument("--grid-channels", default="16,32,64,128,256,512")
@@ -185,8 +188,17 @@ def main():
             rows = sweep(a, clocks)
         elif a.grid:
             rows = grid(a, clocks)
+        elif a.quick:
+            case = build(a.op, a.cin, a.cout, a.size, a.batch, False, not a.no_kd_fused, a.gn_groups)
+            for i in range(6):
+                case.ours(i)
+            torch.cuda.synchronize()
+            _lib.check_status()
+            rows = [{"op": a.op, "label": case.label, "quick": True}]
+            print(f"{a.op} {case.label}: 6 calls done", flush=True)
         else:
-            rows = [run(a.op, a.cin, a.cout, a.size, a.batch, not a.no_ref, not a.no_kd_fused, clocks, a.budget)]
+            rows = [run(a.op, a.cin, a.cout, a.size, a.batch, not a.no_ref, not a.no_kd_fused, clocks, a.budget,
+                        a.gn_groups)]
             print(fmt(rows[-1]), flush=True)
     if a.json and int(os.environ.get("RANK", "0")) == 0:
         Path(a.json).parent.mkdir(parents=True, exist_ok=True)

@@ -39,7 +39,9 @@ def _rot(n: int, make):
     return [make() for _ in range(n)]
 
 
-def conv_case(op: str, cin: int, cout: int, size: int, batch: int, kd_fused: bool = True, library: bool = True) -> Case:
+def conv_case(op: str, cin: int, cout: int, size: int, batch: int, kd_fused: bool = True, library: bool = True,
+              gn_groups: int = 0) -> Case:
+    """``gn_groups`` > 0 (forward only): the kernel also writes the GroupNorm partial statistics of its output."""
     dev = "cuda"
     ci = max(cin, 16)
     n, s = batch, size
@@ -52,7 +54,8 @@ def conv_case(op: str, cin: int, cout: int, size: int, batch: int, kd_fused: boo
     flops = 2.0 * n * s ** 3 * ci * cout * 27
     vox = n * s ** 3
     if op == "conv_fwd":
-        ours = lambda i: ck.conv_same([xs[i % nbuf]], wf, 3, [cout], kd_fused=kd_fused)
+        ours = lambda i: ck.conv_same([xs[i % nbuf]], wf, 3, [cout], kd_fused=kd_fused, gn_groups=gn_groups,
+                                      gn_sink=[] if gn_groups else None)
         gemm = (vox, cout, ci * 27)
     elif op == "conv_dgrad":
         ours = lambda i: ck.conv_same([gys[i % nbuf]], wd, 3, [ci], kd_fused=kd_fused)

@@ -132,7 +132,7 @@ SCHEMA: List[Key] = [
     Key("n_channels", 3, scalar=True, conv=require_positive_int),
     Key("gn_stats", "global", conv=_choice("global", "per_shard")),
     Key("grad_allreduce", "fused", conv=_choice("fused", "nccl")),
-    Key("grad_overlap", False, conv=_flag),
+    Key("grad_overlap", True, conv=_flag),
     Key("halo_exchange", "fused", conv=_choice("fused", "nccl")),
     Key("allow_fallback", False, conv=_flag),
     Key("point_num_override", None, scalar=True),

@@ -368,8 +368,9 @@ class Conv3d(nn.Conv3d):
             vms = [to_vm(t, pad16=True) for t in xs]
             d, h, w = vms[0].shape[1:4]
             real = self._real_in_channels([v.shape[4] for v in vms])
+            # out_channels % 32: the weight-gradient kernel that reads the landed slabs tiles gy by 32 channels
             if h >= 8 and w >= 16 and d >= 2 and self.bias is None and real == [v.shape[4] for v in vms] \
-                    and self.out_channels % 16 == 0:
+                    and self.out_channels % 32 == 0:
                 return _ConvHaloFn.apply(self.weight, self.bias, self, sp.halo_channel, *vms)
         if sp is not None and sp.size > 1 and self.kernel_size[0] > 1:
             halo = self.kernel_size[0] // 2

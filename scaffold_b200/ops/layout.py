@@ -93,15 +93,23 @@ def direct_grad_target(param):
 
 
 def add_grad_written_listener(fn) -> None:
-    _grad_written_listeners.append(fn)
+    """Register a bound method (held weakly: a reducer that is dropped stops listening by itself)."""
+    import weakref
+    _grad_written_listeners.append(weakref.WeakMethod(fn) if hasattr(fn, "__self__") else (lambda f=fn: f))
 
 
 def remove_grad_written_listener(fn) -> None:
-    if fn in _grad_written_listeners:
-        _grad_written_listeners.remove(fn)
+    _grad_written_listeners[:] = [r for r in _grad_written_listeners if r() is not None and r() != fn]
 
 
 def notify_grad_written(param) -> None:
     """Called by a backward pass that wrote ``param.grad`` itself (autograd's accumulate hooks do not fire then)."""
-    for fn in list(_grad_written_listeners):
-        fn(param)
+    dead = False
+    for ref in list(_grad_written_listeners):
+        fn = ref()
+        if fn is None:
+            dead = True
+        else:
+            fn(param)
+    if dead:
+        _grad_written_listeners[:] = [r for r in _grad_written_listeners if r() is not None]

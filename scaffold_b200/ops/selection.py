@@ -29,7 +29,7 @@ def _halo_mode(conv: Conv3d, spatial, src_c: Sequence[int], dims) -> str:
         return "-"
     d, h, w = dims
     chan = getattr(spatial, "halo_channel", None)
-    if (chan is not None and h >= 8 and w >= 16 and d >= 2 and conv.bias is None and conv.out_channels % 16 == 0
+    if (chan is not None and h >= 8 and w >= 16 and d >= 2 and conv.bias is None and conv.out_channels % 32 == 0
             and all(c % 16 == 0 for c in src_c)):
         return "fused(" + ",".join("DHW"[a - 2] for a in spatial.dims) + ")"
     return "nccl slabs"
