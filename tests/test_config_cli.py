@@ -113,6 +113,35 @@ def test_restart_script_rewrites_argv():
 
 def test_grad_overlap_key_and_flag(tmp_path):
     merged = C.load_config_files([str(C.default_config_path())])
-    assert C.Config(dict(merged, base_run_dir=str(tmp_path))).grad_overlap is False
-    args = cli.build_parser().parse_args(["benchmark", "--grad-overlap", "1"])
-    assert "grad_overlap" in cli.explicit_cli_keys(args) and args.grad_overlap == 1
+    assert C.Config(dict(merged, base_run_dir=str(tmp_path))).grad_overlap is True  # on by default; the flag turns it off
+    args = cli.build_parser().parse_args(["benchmark", "--grad-overlap", "0"])
+    assert "grad_overlap" in cli.explicit_cli_keys(args) and args.grad_overlap == 0
+
+
+def test_superset_keys_have_b200_defaults_and_validate(tmp_path):
+    cfg = C.Config(base_dict(tmp_path))
+    assert cfg.grad_allreduce == "fused" and cfg.halo_exchange == "fused"
+    assert cfg.grad_overlap is True and cfg.allow_fallback is False and cfg.datagen_device == "auto"
+    off = C.Config(base_dict(tmp_path, grad_overlap=0, allow_fallback=1, grad_allreduce="nccl", halo_exchange="nccl",
+                             gn_stats="per_shard", unet_base_width=32))
+    assert off.grad_overlap is False and off.allow_fallback is True and off.unet_base_width == 32
+    for bad in (dict(grad_allreduce="mpi"), dict(halo_exchange="rdma"), dict(unet_base_width=0),
+                dict(datagen_device="tpu")):
+        with pytest.raises((ValueError, KeyError)):
+            C.Config(base_dict(tmp_path, **bad))
+
+
+@pytest.mark.parametrize("scale,bottleneck,layers", [(7, 3, 4), (8, 3, 5), (9, 3, 6), (5, 2, 3)])
+def test_network_depth_follows_scale_and_bottleneck(tmp_path, scale, bottleneck, layers):
+    cfg = C.Config(base_dict(tmp_path, problem_scale=scale, unet_bottleneck_dim=bottleneck))
+    assert cfg.unet_layers == layers and cfg.vol_size == 2 ** scale
+
+
+def test_cli_flags_for_the_fused_paths_reach_the_config(tmp_path):
+    base = tmp_path / "b.yml"
+    base.write_text(yaml.safe_dump(base_dict(tmp_path, problem_scale=5)))
+    parser = cli.build_parser()
+    ns = parser.parse_args(["benchmark", "-c", str(base), "--grad-overlap", "0", "--allow-fallback", "1",
+                            "--halo-exchange", "nccl", "--dc-num-shards", "1", "1", "2"])
+    assert ns.grad_overlap == 0 and ns.allow_fallback == 1 and ns.halo_exchange == "nccl"
+    assert ns.dc_num_shards == [1, 1, 2]
