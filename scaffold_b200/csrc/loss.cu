@@ -101,11 +101,9 @@ __global__ void __launch_bounds__(LOSS_THREADS) loss_sums_kernel(const __nv_bflo
 #pragma unroll
   for (int c = 0; c < CP; ++c) { P[c] = 0.f; Q[c] = 0.f; I[c] = 0.f; }
   float ce_num = 0.f, ce_den = 0.f;
-  for (long long v = (long long)blockIdx.x * LOSS_THREADS + threadIdx.x; v < S;
-       v += (long long)gridDim.x * LOSS_THREADS) {
-    float f[CP];
-    load_logits<CP>(logits + ((long long)n * S + v) * CP, f);
-    const long long y_raw = load_label(labels, label_kind, (long long)n * S + v);
+  // two voxels per iteration: both voxels' logits and labels are requested before either is used
+  const long long stride = (long long)gridDim.x * LOSS_THREADS;
+  auto voxel = [&](float (&f)[CP], const long long y_raw) {
     const bool y_ok = y_raw >= 0 && y_raw < C;
     const int y = y_ok ? (int)y_raw : -1;
     if (!y_ok) report(status, ST_BAD_ARG, 61, (uint32_t)y_raw, (uint32_t)n);
@@ -132,6 +130,21 @@ __global__ void __launch_bounds__(LOSS_THREADS) loss_sums_kernel(const __nv_bflo
     const float wy = y_ok ? (cw ? cw[y] : 1.f) : 0.f;
     ce_num += wy * (lse - ly);
     ce_den += wy;
+  };
+  long long v = (long long)blockIdx.x * LOSS_THREADS + threadIdx.x;
+  for (; v + stride < S; v += 2 * stride) {
+    float f0[CP], f1[CP];
+    load_logits<CP>(logits + ((long long)n * S + v) * CP, f0);
+    load_logits<CP>(logits + ((long long)n * S + v + stride) * CP, f1);
+    const long long y0 = load_label(labels, label_kind, (long long)n * S + v);
+    const long long y1 = load_label(labels, label_kind, (long long)n * S + v + stride);
+    voxel(f0, y0);
+    voxel(f1, y1);
+  }
+  for (; v < S; v += stride) {
+    float f0[CP];
+    load_logits<CP>(logits + ((long long)n * S + v) * CP, f0);
+    voxel(f0, load_label(labels, label_kind, (long long)n * S + v));
   }
   float* dst = ws + ((long long)n * gridDim.x + blockIdx.x) * (3 * C + 2);
 #pragma unroll
@@ -177,12 +190,7 @@ __global__ void __launch_bounds__(LOSS_THREADS) loss_grad_kernel(const __nv_bflo
     beta[c] = c < C ? coef[((long long)n * 2 + 1) * C + c] : 0.f;
   }
   const float k_ce = kce[0];
-  for (long long v = (long long)blockIdx.x * LOSS_THREADS + threadIdx.x; v < S;
-       v += (long long)gridDim.x * LOSS_THREADS) {
-    float f[CP];
-    const long long off = ((long long)n * S + v) * CP;
-    load_logits<CP>(logits + off, f);
-    const long long y_raw = load_label(labels, label_kind, (long long)n * S + v);
+  auto voxel = [&](float (&f)[CP], const long long y_raw, const long long off) {
     const bool y_ok = y_raw >= 0 && y_raw < C;
     const int y = y_ok ? (int)y_raw : -1;
     if (!y_ok) report(status, ST_BAD_ARG, 62, (uint32_t)y_raw, (uint32_t)n);
@@ -209,6 +217,25 @@ __global__ void __launch_bounds__(LOSS_THREADS) loss_grad_kernel(const __nv_bflo
       o.w = pack_bf16x2(g[i * 8 + 6], g[i * 8 + 7]);
       reinterpret_cast<uint4*>(dlogits + off)[i] = o;
     }
+  };
+  // two voxels per iteration: both voxels' logits and labels are requested before either is used
+  const long long stride = (long long)gridDim.x * LOSS_THREADS;
+  long long v = (long long)blockIdx.x * LOSS_THREADS + threadIdx.x;
+  for (; v + stride < S; v += 2 * stride) {
+    float f0[CP], f1[CP];
+    const long long off0 = ((long long)n * S + v) * CP, off1 = ((long long)n * S + v + stride) * CP;
+    load_logits<CP>(logits + off0, f0);
+    load_logits<CP>(logits + off1, f1);
+    const long long y0 = load_label(labels, label_kind, (long long)n * S + v);
+    const long long y1 = load_label(labels, label_kind, (long long)n * S + v + stride);
+    voxel(f0, y0, off0);
+    voxel(f1, y1, off1);
+  }
+  for (; v < S; v += stride) {
+    float f0[CP];
+    const long long off0 = ((long long)n * S + v) * CP;
+    load_logits<CP>(logits + off0, f0);
+    voxel(f0, load_label(labels, label_kind, (long long)n * S + v), off0);
   }
 }
 
