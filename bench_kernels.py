@@ -168,6 +168,8 @@ def main():
     ap.add_argument("--gn-groups", type=int, default=0, help="conv_fwd: also produce GroupNorm statistics in the epilogue")
     ap.add_argument("--quick", action="store_true",
                     help="a handful of calls of our kernel only, no pairing loop (the form to run under a profiler)")
+    ap.add_argument("--iters", type=int, default=0,
+                    help="like --quick with 3 warm-up calls + this many calls (the fixed-iteration form of older profiles)")
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--grid", action="store_true")
     ap.add_argument("--grid-channels", default="16,32,64,128,256,512")
@@ -188,14 +190,14 @@ def main():
             rows = sweep(a, clocks)
         elif a.grid:
             rows = grid(a, clocks)
-        elif a.quick:
+        elif a.quick or a.iters > 0:
             case = build(a.op, a.cin, a.cout, a.size, a.batch, False, not a.no_kd_fused, a.gn_groups)
-            for i in range(6):
+            for i in range(3 + a.iters if a.iters > 0 else 6):
                 case.ours(i)
             torch.cuda.synchronize()
             _lib.check_status()
             rows = [{"op": a.op, "label": case.label, "quick": True}]
-            print(f"{a.op} {case.label}: 6 calls done", flush=True)
+            print(f"{a.op} {case.label}: calls done", flush=True)
         else:
             rows = [run(a.op, a.cin, a.cout, a.size, a.batch, not a.no_ref, not a.no_kd_fused, clocks, a.budget,
                         a.gn_groups)]
