@@ -137,8 +137,9 @@ class ConvProblem:
         cin = sum(sc) if sc else _pad(self.cin)
         return replace(self, cin=cin, cout=_pad(self.cout), split_cin=sc)
 
-    def route(self, direction: Direction = "fwd") -> str:
-        """Name of the kernel that runs this problem (mirrors the dispatch in csrc/conv_igemm.cu / conv_wgrad.cu)."""
+    def route(self, direction: Direction = "fwd", pair: bool = True) -> str:
+        """Name of the kernel that runs this problem (mirrors the dispatch in csrc/conv_igemm.cu / conv_wgrad.cu);
+        ``pair=False`` gives the routing with the two-SM kernel switched off."""
         k = self.kernel_variant()
         d, h, w = k.out_spatial if direction != "dgrad" else k.spatial
         if self.transposed:
@@ -154,6 +155,8 @@ class ConvProblem:
             return "wgrad_plane" if big else "wgrad(generic)"
         rows, kk = (k.cout, k.cin) if direction == "fwd" else (k.cin, k.cout)
         first = (k.split_cin[0] if (k.split_cin and direction == "fwd") else kk)
+        if big and pair and rows >= 128 and rows % 128 == 0 and kk % 64 == 0 and first % 64 == 0:
+            return "conv_plane2(pair)"  # two-SM cta_group::2 kernel, with or without a fused halo
         if big and (rows <= 64 or rows % 64 == 0) and kk % 32 == 0 and first % 32 == 0:
             return "conv_plane3"
         return "conv_plane" if big else "igemm"

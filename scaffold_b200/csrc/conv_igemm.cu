@@ -423,6 +423,7 @@ using namespace sb;
 // packs the weights transposed and tap-flipped.
 namespace sb {
 int conv_plane_launch(const SbConvArgs* a, cudaStream_t stream);
+int conv_plane2_launch(const SbConvArgs* a, cudaStream_t stream);
 int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream);
 int conv_plane3_gn_splits(const SbConvArgs* a);
 int conv_small_launch(const SbConvArgs* a, cudaStream_t stream);
@@ -430,21 +431,28 @@ long long conv_small_workspace(const SbConvArgs* a);
 }
 
 // fp32 scratch elements sb_conv_fwd wants for this call (0: none)
+static bool automatic(const SbConvArgs* a) { return a->force_plain == 0 || a->force_plain == 4; }
+
 extern "C" long long sb_conv_fwd_workspace(const SbConvArgs* a) {
-  return a->force_plain == 0 ? conv_small_workspace(a) : 0;
+  return automatic(a) ? conv_small_workspace(a) : 0;
 }
 
 extern "C" int sb_conv_gn_splits(const SbConvArgs* a) {
-  return a->force_plain == 0 ? conv_plane3_gn_splits(a) : 0;
+  return automatic(a) ? conv_plane3_gn_splits(a) : 0;
 }
 
-// force_plain: 0 = automatic (8 x 8 plane kernel, kd-fused or plane-walk kernel when the shape is eligible, else
-// this file's generic kernel), 1 = generic kernel one tap per load, 2 = generic kernel with the w-shift
-// reuse, 3 = generic kernel with the (h, w)-shift reuse.
+// force_plain: 0 = automatic (8 x 8 plane kernel; the two-SM pair kernel for wide outputs given tap-ordered
+// weights only; kd-fused or plane-walk kernel when the shape is eligible; else this file's generic kernel),
+// 1 = generic kernel one tap per load, 2 = generic kernel with the w-shift reuse, 3 = generic kernel with the
+// (h, w)-shift reuse, 4 = automatic without the pair kernel.
 extern "C" int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream) {
-  if (a->force_plain == 0) {
+  if (automatic(a)) {
     const int sm = conv_small_launch(a, stream);
     if (sm >= 0) return sm;
+    if (a->force_plain == 0 && a->wpack_kd == nullptr && a->gn_part == nullptr) {
+      const int p2 = conv_plane2_launch(a, stream);
+      if (p2 >= 0) return p2;
+    }
     const int p3 = conv_plane3_launch(a, stream);
     if (p3 >= 0) return p3;
     if (a->gn_part != nullptr) return SB_ERR_SHAPE;  // statistics come from the kd-fused kernel only

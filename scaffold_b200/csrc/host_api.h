@@ -35,7 +35,7 @@ typedef struct {
   int dst_ld[2];  // channel stride of each destination
   const float* bias;  // optional, added to destination 0 columns
   uint32_t* status;   // optional 4-word status block
-  int force_plain;    // tests: 0 automatic, 1..3 select a variant of the generic kernel
+  int force_plain;    // 0 automatic, 1..3 select a variant of the generic kernel, 4 automatic without the pair kernel
   // Spatially sharded volumes: the sources may carry a halo. in_* are the sources' spatial
   // extents (0 = same as D/H/W) and off_* the position of output voxel 0 inside them, so
   // input coordinate = output coordinate + tap - k/2 + off (negative offsets read zeros).

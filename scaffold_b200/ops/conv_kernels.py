@@ -7,6 +7,8 @@ module parameters and the CPU path live in :mod:`scaffold_b200.ops.conv3d`.
 """
 from __future__ import annotations
 
+import os
+
 import ctypes as C
 from typing import Optional, Sequence
 
@@ -68,10 +70,27 @@ class Packed:
         self.shape = (std if std is not None else kd).shape
 
 
-def kd_eligible(rows: int, k: int, out_dims: Sequence[int], first_src: Optional[int] = None) -> bool:
-    """True when ``sb_conv_fwd`` runs the kd-fused plane kernel for this call (no fused halo / slabs)."""
+# Wide-output 3x3x3 calls run on SM pairs (tcgen05 cta_group::2, csrc/conv_plane2.cu). SCAFFOLD_PAIR_CONV=0 keeps
+# them on the single-CTA kernels (the A/B switch of the kernel benchmarks).
+PAIR_CONV = os.environ.get("SCAFFOLD_PAIR_CONV", "1") != "0"
+
+
+def pair_eligible(rows: int, k: int, out_dims: Sequence[int], first_src: Optional[int] = None) -> bool:
+    """True when ``sb_conv_fwd`` runs the two-SM pair kernel for a call that passes tap-ordered weights only:
+    >= 128 output rows in multiples of 128, sources in multiples of 64 channels, planes of at least 8 x 16."""
     _, h, w = out_dims
     first = k if first_src is None else first_src
+    return (PAIR_CONV and w >= 16 and h >= 8 and rows >= 128 and rows % 128 == 0 and k % 64 == 0
+            and first % 64 == 0)
+
+
+def kd_eligible(rows: int, k: int, out_dims: Sequence[int], first_src: Optional[int] = None) -> bool:
+    """True when ``sb_conv_fwd`` should get the kd-ordered weights and run the kd-fused plane kernel for this
+    call (no fused halo / slabs); wide outputs go to the pair kernel instead."""
+    _, h, w = out_dims
+    first = k if first_src is None else first_src
+    if pair_eligible(rows, k, out_dims, first_src):
+        return False
     return (w >= 16 and h >= 8 and rows % 16 == 0 and (rows <= 64 or rows % 64 == 0) and k % 32 == 0
             and first % 32 == 0)
 
@@ -181,6 +200,9 @@ def conv_same(srcs: Sequence[torch.Tensor], wpack: torch.Tensor, ksize: int,
         std, kd = wpack.std, (wpack.kd if kd_fused else None)
     else:
         std, kd = wpack, (getattr(wpack, "kd_order", None) if kd_fused else None)
+    if kd is not None and std is not None and pair_eligible(wpack.shape[1], wpack.shape[2], (d, h, w),
+                                                            srcs[0].shape[4]):
+        kd = None  # both orderings at hand: the pair kernel reads the tap-ordered one
     a.wpack = std.data_ptr() if std is not None else None
     a.cout_pad = wpack.shape[1]
     a.wpack_kd = kd.data_ptr() if kd is not None else None
@@ -199,7 +221,7 @@ def conv_same(srcs: Sequence[torch.Tensor], wpack: torch.Tensor, ksize: int,
             a.dst_ld[i] = 0
     a.bias = _lib.ptr(bias)
     a.status = _lib.status_tensor(srcs[0].device).data_ptr()
-    a.force_plain = int(force_plain)
+    a.force_plain = int(force_plain) if (PAIR_CONV or int(force_plain) != 0) else 4
     if halo is not None:
         # fused depth halo: landing slabs per (source, face) and the flag words that guard them
         for si in range(len(srcs)):

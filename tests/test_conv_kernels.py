@@ -41,7 +41,7 @@ def pad_c(x, c):  # pad channel dim (dim 1) of NCDHW with zeros
 
 FWD_CASES = [
     # N, D, H, W, Cin(list), Cout, k, kernel mode (0 auto: kd-fused plane kernel for <= 64 output channels else
-    # plane-walk, 1 plain, 2 w-shift, 3 hw-shift, 4 plane-walk without kd fusion)
+    # plane-walk, 1 plain, 2 w-shift, 3 hw-shift, 4 single-CTA plane-walk: no kd fusion, no pair kernel)
     (1, 4, 16, 32, [64], 64, 3, 4),
     (2, 7, 24, 48, [64], 64, 3, 4),
     (1, 2, 16, 16, [64, 64], 64, 3, 4),
@@ -99,8 +99,7 @@ def test_conv_fwd_bitwise(case):
     if bias is not None:
         bpad = torch.zeros(cpad, device="cuda")
         bpad[:cout] = bias
-    (y,) = ck.conv_same(srcs, wpack, k, [cpad], bias=bpad, force_plain=0 if plain == 4 else plain,
-                        kd_fused=plain != 4)
+    (y,) = ck.conv_same(srcs, wpack, k, [cpad], bias=bpad, force_plain=plain, kd_fused=plain != 4)
     torch.cuda.synchronize()
     _lib.check_status()
     got = ncdhw(y)[:, :cout]
