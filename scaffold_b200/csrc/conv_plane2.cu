@@ -519,8 +519,7 @@ static int p2_setup() {
 
 static int cdiv_p2(int a, int b) { return (a + b - 1) / b; }
 
-// Shape rule of the pair kernel; the launcher and the kernel-selection report share it.
-// Returns BN (128 or 256) when the call is eligible, else 0.
+// Shape rule of the pair kernel. Returns the widest tile (128 or 256) the call admits, 0 when it is not eligible.
 int conv_plane2_bn(const SbConvArgs* a) {
   if (a->ksize != 3 || a->W < 16 || a->H < 8 || a->wpack == nullptr) return 0;
   if (a->cout_pad < 128 || a->cout_pad % 128 != 0) return 0;
@@ -531,49 +530,65 @@ int conv_plane2_bn(const SbConvArgs* a) {
   return a->cout_pad % 256 == 0 ? 256 : 128;
 }
 
+// Tile width BN and job depth TD (output planes that share one set of weight taps) by a cost model fitted to
+// measurements on B200:  time ~ waves x (MMA cycles of a job x penalty + exposed epilogue), where
+//   waves   = ceil(pair-jobs / SM pairs)               (small volumes: more, smaller jobs fill the machine)
+//   penalty = 1.4 for (BN 128, TD 1): an 8 KB weight tap then feeds only four MMAs and the loop starves on
+//             weight-tile traffic; 1.05 for (128, 2); 1.0 otherwise
+//   exposed epilogue = TD x BN x 5 cycles when the accumulators cannot double-buffer (TD x BN = 512 columns).
+// Ties go to the wider tile, then to the deeper job. Returns false when nothing fits.
+static bool p2_choose(const SbConvArgs* a, int bn_max, int cblks, int clusters, int a_slot_bytes, int smem_budget,
+                      int* bn_out, int* td_out) {
+  const int tiles_h = cdiv_p2(a->H, 8), tiles_w = cdiv_p2(a->W, 16);
+  double best = 0.0;
+  bool found = false;
+  for (int bn = bn_max; bn >= 128; bn /= 2) {
+    const int b_slot_bytes = (bn / 2) * P2_ROWB;
+    for (int td = 512 / bn; td >= 1; td /= 2) {
+      if (td > a->D && td > 1) continue;
+      if ((td + 2) * a_slot_bytes + 3 * b_slot_bytes > smem_budget) continue;
+      const long long tl = (long long)a->N * cdiv_p2(a->D, td) * tiles_h * tiles_w;
+      const long long jobs = ((tl + 1) / 2) * (a->cout_pad / bn);
+      const long long waves = (jobs + clusters - 1) / clusters;
+      const double penalty = bn == 128 ? (td == 1 ? 1.4 : td == 2 ? 1.05 : 1.0) : 1.0;
+      const double mma = (double)cblks * 27.0 * td * P2_KSTEPS * (bn / 2) * penalty;
+      const double epi = (td * bn == 512) ? td * bn * 5.0 : 0.0;
+      const double cost = (double)waves * (mma + epi);
+      if (!found || cost < best * 0.999) {
+        best = cost;
+        *bn_out = bn;
+        *td_out = td;
+        found = true;
+      }
+    }
+  }
+  return found;
+}
+
 // Returns -1 when the shape is not eligible (the caller then uses the single-CTA kernels).
 int conv_plane2_launch(const SbConvArgs* a, cudaStream_t stream) {
-  const int bn = conv_plane2_bn(a);
-  if (bn == 0) return -1;
+  const int bn_max = conv_plane2_bn(a);
+  if (bn_max == 0) return -1;
   int rc = p2_setup();
   if (rc) return rc;
   Plane2Params p;
   memset(&p, 0, sizeof(p));
   const int cin_tot = a->src_c[0] + a->src_c[1];
   const int nsrc = a->src_c[1] > 0 ? 2 : 1;
-  p.BN = bn;
+  const int rowb = P2_ROWB;
+  const int clusters = g_p2_clusters;
+  const int cblks = cin_tot / P2_BK;
+  p.a_tx = P2_RH * P2_RW * rowb;
+  p.a_slot_bytes = ((p.a_tx + 1023) / 1024) * 1024;
+  int td = 1;
+  if (!p2_choose(a, bn_max, cblks, clusters, p.a_slot_bytes, g_p2_smem - 1024, &p.BN, &td)) return -1;
   p.N = a->N; p.D = a->D; p.H = a->H; p.W = a->W;
   p.tiles_h = cdiv_p2(a->H, 8);
   p.tiles_w = cdiv_p2(a->W, 16);
   p.tiles_co = a->cout_pad / p.BN;
-  const int rowb = P2_ROWB;
-  p.a_tx = P2_RH * P2_RW * rowb;
-  p.a_slot_bytes = ((p.a_tx + 1023) / 1024) * 1024;
   p.b_tx = (p.BN / 2) * rowb;
   p.b_slot_bytes = ((p.b_tx + 1023) / 1024) * 1024;
   const int max_acc = 512 / p.BN;
-  const int clusters = g_p2_clusters;
-  // Depth of the job (output planes that share one set of weight taps). Measured on B200: with BN = 128 a
-  // depth of 1 starves on weight-tile traffic (each 8 KB tap feeds only four MMAs), so depth 4 when the
-  // reduction has at least two channel blocks, else 2 (the accumulators then double-buffer and the
-  // epilogue hides behind the short main loop); halved only while fewer than half of the SM pairs
-  // would get a job. With BN = 256 two accumulators fill TMEM: depth 2, or 1 when depth 2 leaves
-  // fewer than 1.5 jobs per pair.
-  const int cblks = cin_tot / P2_BK;
-  auto jobs_at = [&](int t) {
-    const long long tl = (long long)a->N * cdiv_p2(a->D, t) * p.tiles_h * p.tiles_w;
-    return ((tl + 1) / 2) * p.tiles_co;
-  };
-  int td;
-  if (p.BN == 128) {
-    td = cblks >= 2 ? 4 : 2;
-    while (td > 1 && td > a->D) td /= 2;
-    while (td > 2 && jobs_at(td) * 2 < clusters) td /= 2;
-  } else {
-    td = (a->D >= 2 && jobs_at(2) * 2 >= 3LL * clusters) ? 2 : 1;
-  }
-  while (td > 1 && (td + 2) * p.a_slot_bytes + 3 * p.b_slot_bytes > g_p2_smem - 1024) td /= 2;
-  if (td > max_acc) td = max_acc;
   p.TD = td;
   p.n_bufs = max_acc / td >= 2 ? 2 : 1;
   p.groups_d = cdiv_p2(a->D, td);
@@ -660,3 +675,16 @@ int conv_plane2_launch(const SbConvArgs* a, cudaStream_t stream) {
 }
 
 }  // namespace sb
+
+// Tile width and job depth the pair kernel would use for this call on a device with `clusters` SM pairs
+// (no device needed: the host-side tests pin the selection). Returns 0 and fills bn / td, or -1 when the
+// call is not eligible.
+extern "C" int sb_conv_pair_plan(const SbConvArgs* a, int clusters, int* bn, int* td) {
+  const int bn_max = sb::conv_plane2_bn(a);
+  if (bn_max == 0 || clusters < 1) return -1;
+  const int cblks = (a->src_c[0] + a->src_c[1]) / sb::P2_BK;
+  const int a_tx = sb::P2_RH * sb::P2_RW * sb::P2_ROWB;
+  const int a_slot_bytes = ((a_tx + 1023) / 1024) * 1024;
+  const int budget = 232448 - 2048 - 1024;  // opt-in shared memory of an sm_100 CTA less the launcher's reserve
+  return sb::p2_choose(a, bn_max, cblks, clusters, a_slot_bytes, budget, bn, td) ? 0 : -1;
+}

@@ -180,6 +180,8 @@ int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream);
 long long sb_conv_fwd_workspace(const SbConvArgs* a);
 // splits per sample of the statistics the call would write into gn_part; 0 = this call cannot produce them
 int sb_conv_gn_splits(const SbConvArgs* a);
+// tile width / job depth of the two-SM pair kernel for this call (-1: not eligible); needs no device
+int sb_conv_pair_plan(const SbConvArgs* a, int clusters, int* bn, int* td);
 int sb_convT_fwd(const SbConvTArgs* a, cudaStream_t stream);
 int sb_convT_dgrad(const SbConvTArgs* a, cudaStream_t stream);
 int sb_conv_wgrad(const SbWgradArgs* a, cudaStream_t stream);

@@ -146,6 +146,7 @@ _SIGNATURES = {
     "sb_conv_fwd": ([C.POINTER(SbConvArgs), _P], C.c_int),
     "sb_conv_fwd_workspace": ([C.POINTER(SbConvArgs)], C.c_longlong),
     "sb_conv_gn_splits": ([C.POINTER(SbConvArgs)], C.c_int),
+    "sb_conv_pair_plan": ([C.POINTER(SbConvArgs), C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)], C.c_int),
     "sb_pack_conv3": ([C.POINTER(SbPackArgs), _P], C.c_int),
     "sb_pack_conv3_plan": ([C.POINTER(SbPackJob), C.c_int], C.c_longlong),
     "sb_pack_conv3_batch": ([_P, C.c_int, C.c_longlong, _P], C.c_int),
