@@ -19,6 +19,7 @@ import torch
 import torch.nn as nn
 
 from ..analysis.shapes import ConvProblem
+from . import conv_kernels as ck
 from .conv3d import Conv3d, ConvTranspose3d
 from .group_norm import GroupNorm
 from .pool import MaxPool3d
@@ -55,7 +56,7 @@ def kernel_selection(model: nn.Module, batch: int, local_dims: Sequence[int], sp
             split = (c // 2, c - c // 2) if mod in split_first else None
             p = ConvProblem(n, c, mod.out_channels, (d, h, w), kernel=mod.kernel_size[0], split_cin=split)
             halo = _halo_mode(mod, spatial, split or (p.kernel_variant().cin,), (d, h, w))
-        fwd, dgrad = p.route("fwd"), p.route("dgrad")
+        fwd, dgrad = p.route("fwd", ck.PAIR_CONV), p.route("dgrad", ck.PAIR_CONV)
         if not p.transposed and c < 16:
             # the stem: its forward pass reads a copy padded to 32 channels, and the network input needs no gradient
             fwd = ConvProblem(n, 32, mod.out_channels, (d, h, w), kernel=p.kernel).route("fwd") + " (32-ch padded input)"

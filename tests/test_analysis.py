@@ -52,6 +52,12 @@ def test_conv_problem_cost_model():
     assert p.gemm_shape("wgrad") == (64, 64 * 27, 2 * 128 ** 3)
     assert p.route("fwd") == "conv_plane3" and p.route("wgrad") == "wgrad_plane"
     assert S.ConvProblem(2, 3, 64, (128, 128, 128)).route("fwd") == "conv_plane"   # 16 padded channels
+    wide = S.ConvProblem(2, 128, 256, (32, 32, 32))
+    assert wide.route("fwd") == "conv_plane2(pair)" and wide.route("fwd", pair=False) == "conv_plane3"
+    assert wide.route("dgrad") == "conv_plane2(pair)"           # backward-data rows = C_in = 128
+    assert S.ConvProblem(2, 128, 64, (128, 128, 128)).route("fwd") == "conv_plane3"     # 64 output rows
+    assert S.ConvProblem(2, 128, 64, (128, 128, 128)).route("dgrad") == "conv_plane2(pair)"
+    assert S.ConvProblem(2, 96, 128, (32, 32, 32)).route("fwd") == "conv_plane3"        # sources not in 64s
     assert S.ConvProblem(2, 512, 1024, (8, 8, 8)).route("fwd") == "conv_small"
     assert S.ConvProblem(2, 64, 128, (4, 4, 4)).route("fwd") == "igemm"
     t = S.ConvProblem(1, 128, 64, (4, 8, 16), 2, True)
