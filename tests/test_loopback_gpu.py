@@ -25,7 +25,10 @@ def _ints(shape, lo, hi, g):
     return torch.randint(lo, hi + 1, shape, generator=g, device="cuda").to(torch.bfloat16)
 
 
-@pytest.mark.parametrize("cin,cout,dims", [(64, 64, (8, 16, 32)), (32, 128, (4, 8, 16))])
+# the last two cases run the two-SM pair kernel: forward with landing slabs (>= 128 output rows), and for 128 -> 256
+# also backward-data with slab outputs (128 rows)
+@pytest.mark.parametrize("cin,cout,dims", [(64, 64, (8, 16, 32)), (32, 128, (4, 8, 16)), (64, 128, (4, 8, 16)),
+                                           (128, 256, (6, 16, 16))])
 def test_halo_push_then_conv_forward_dgrad_wgrad_match_the_whole_volume(cin, cout, dims):
     _lib, ck, gk = _mods()
     g = torch.Generator(device="cuda").manual_seed(3)
