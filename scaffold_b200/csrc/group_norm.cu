@@ -21,6 +21,8 @@
 // all global accesses are full coalesced 16-byte vectors.
 //
 // Role of the reference: ScaFFold/unet/triton_group_norm.py:594-1043.
+#include <atomic>
+
 #include "common.cuh"
 #include "host_api.h"
 
@@ -38,6 +40,8 @@ struct GnParams {
   float* mean;   // [N, G]
   float* rstd;   // [N, G]
   float* part;   // this rank's partials
+  float* fin;    // optional: the last block of a statistics / backward-sums launch also collapses the partials here
+  unsigned int* ticket;  // block counter of that hand-over (zero before the launch, reset by the last block)
   const float* parts[GN_MAX_PARTS];  // partial buffers to merge (own first)
   int n_parts;
   float* dw;     // [C]
@@ -81,6 +85,71 @@ __device__ __forceinline__ void chan_merge(float& n_a, float& mean_a, float& m2_
   mean_a += delta * r;
   m2_a += m2_b + delta * delta * n_a * r;
   n_a = n;
+}
+
+
+// One warp collapses the `nsplit` partials of (n, g) with a fixed merge tree (lane-strided, then xor
+// shuffles merging the lower lane first): the separate finalize kernel and the last-block tail of the
+// statistics kernel run exactly this, so both give the same bits. Loads bypass L1 (the partials may
+// have been written by other SMs during this launch).
+__device__ __forceinline__ void stats_collapse_warp(const float* __restrict__ part, float* __restrict__ fin, int G,
+                                                    int nsplit, int n, int g, int lane) {
+  float gn = 0.f, gm = 0.f, g2 = 0.f;
+  for (int s = lane; s < nsplit; s += 32) {
+    const float* e = part + (((long long)n * nsplit + s) * G + g) * 3;
+    chan_merge(gn, gm, g2, __ldcg(e), __ldcg(e + 1), __ldcg(e + 2));
+  }
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float on = __shfl_xor_sync(0xffffffffu, gn, o);
+    const float om = __shfl_xor_sync(0xffffffffu, gm, o);
+    const float o2 = __shfl_xor_sync(0xffffffffu, g2, o);
+    // merge (lower lane, higher lane) in that order on both sides: bitwise identical results
+    if (lane & o) {
+      float an = on, am = om, a2 = o2;
+      chan_merge(an, am, a2, gn, gm, g2);
+      gn = an; gm = am; g2 = a2;
+    } else {
+      chan_merge(gn, gm, g2, on, om, o2);
+    }
+  }
+  if (lane == 0) {
+    float* dst = fin + ((long long)n * G + g) * 3;
+    dst[0] = gn; dst[1] = gm; dst[2] = g2;
+  }
+}
+
+__device__ __forceinline__ void bwd_collapse_warp(const float* __restrict__ part, float* __restrict__ fin, int C,
+                                                  int nsplit, int n, int c, int lane) {
+  float a = 0.f, b = 0.f;
+  for (int s = lane; s < nsplit; s += 32) {
+    const float2 e = __ldcg(reinterpret_cast<const float2*>(part + (((long long)n * nsplit + s) * C + c) * 2));
+    a += e.x;
+    b += e.y;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    b += __shfl_xor_sync(0xffffffffu, b, o);
+  }
+  if (lane == 0) {
+    float* dst = fin + ((long long)n * C + c) * 2;
+    dst[0] = a; dst[1] = b;
+  }
+}
+
+// True in every thread of the block that finished last (all blocks' global writes are then visible to it).
+__device__ __forceinline__ bool last_block_done(unsigned int* ticket) {
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int total = gridDim.x * gridDim.y;
+    s_last = atomicAdd(ticket, 1u) == total - 1u ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_last) __threadfence();
+  return s_last != 0;
 }
 
 // ----------------------------------------------------------------------------
@@ -160,6 +229,13 @@ __global__ void __launch_bounds__(GN_THREADS) gn_stats_kernel(const GnParams p) 
     dst[0] = gn;
     dst[1] = gm;
     dst[2] = g2;
+  }
+  if (p.fin != nullptr && last_block_done(p.ticket)) {
+    // the last block to finish collapses every (n, g): no separate finalize launch
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int o = warp; o < p.N * p.G; o += GN_THREADS / 32)
+      stats_collapse_warp(p.part, p.fin, p.G, p.nsplit, o / p.G, o % p.G, lane);
+    if (threadIdx.x == 0) *p.ticket = 0u;
   }
 }
 
@@ -328,6 +404,12 @@ __global__ void __launch_bounds__(GN_THREADS) gn_bwd_partial_kernel(const GnPara
     dst[0] = sa;
     dst[1] = sbv;
   }
+  if (p.fin != nullptr && last_block_done(p.ticket)) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int o = warp; o < p.N * p.C; o += GN_THREADS / 32)
+      bwd_collapse_warp(p.part, p.fin, p.C, p.nsplit, o / p.C, o % p.C, lane);
+    if (threadIdx.x == 0) *p.ticket = 0u;
+  }
 }
 
 // ----------------------------------------------------------------------------
@@ -444,30 +526,7 @@ __global__ void __launch_bounds__(GN_THREADS) gn_stats_finalize_kernel(const flo
   const int warp = (blockIdx.x * GN_THREADS + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= N * G) return;
-  const int n = warp / G, g = warp % G;
-  float gn = 0.f, gm = 0.f, g2 = 0.f;
-  for (int s = lane; s < nsplit; s += 32) {
-    const float* e = part + (((long long)n * nsplit + s) * G + g) * 3;
-    chan_merge(gn, gm, g2, e[0], e[1], e[2]);
-  }
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const float on = __shfl_xor_sync(0xffffffffu, gn, o);
-    const float om = __shfl_xor_sync(0xffffffffu, gm, o);
-    const float o2 = __shfl_xor_sync(0xffffffffu, g2, o);
-    // merge (lower lane, higher lane) in that order on both sides: bitwise identical results
-    if (lane & o) {
-      float an = on, am = om, a2 = o2;
-      chan_merge(an, am, a2, gn, gm, g2);
-      gn = an; gm = am; g2 = a2;
-    } else {
-      chan_merge(gn, gm, g2, on, om, o2);
-    }
-  }
-  if (lane == 0) {
-    float* dst = fin + ((long long)n * G + g) * 3;
-    dst[0] = gn; dst[1] = gm; dst[2] = g2;
-  }
+  stats_collapse_warp(part, fin, G, nsplit, warp / G, warp % G, lane);
 }
 
 // The same collapse for MANY partials per (n, g) (the per-warp partials a convolution's epilogue leaves: up to
@@ -518,22 +577,7 @@ __global__ void __launch_bounds__(GN_THREADS) gn_bwd_finalize_kernel(const float
   const int warp = (blockIdx.x * GN_THREADS + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= N * C) return;
-  const int n = warp / C, c = warp % C;
-  float a = 0.f, b = 0.f;
-  for (int s = lane; s < nsplit; s += 32) {
-    const float2 e = *reinterpret_cast<const float2*>(part + (((long long)n * nsplit + s) * C + c) * 2);
-    a += e.x;
-    b += e.y;
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    a += __shfl_xor_sync(0xffffffffu, a, o);
-    b += __shfl_xor_sync(0xffffffffu, b, o);
-  }
-  if (lane == 0) {
-    float* dst = fin + ((long long)n * C + c) * 2;
-    dst[0] = a; dst[1] = b;
-  }
+  bwd_collapse_warp(part, fin, C, nsplit, warp / C, warp % C, lane);
 }
 
 // Channel / group counts the kernels cover: C a multiple of 8 in [8, 2048] (one thread per channel
@@ -557,6 +601,7 @@ static int gn_fill(const SbGnArgs* a, GnParams& p) {
   p.y = (__nv_bfloat16*)a->y;
   p.w = a->w; p.b = a->b; p.mean = a->mean; p.rstd = a->rstd;
   p.part = a->part;
+  p.fin = a->fin;
   for (int i = 0; i < a->n_parts; ++i) p.parts[i] = a->parts[i];
   p.n_parts = a->n_parts;
   p.dw = a->dw; p.db = a->db;
@@ -570,6 +615,23 @@ static int gn_fill(const SbGnArgs* a, GnParams& p) {
   p.wait_ticks = (long long)((a->wait_s > 0 ? a->wait_s : 2.0) * 1.8e9);
   p.status = a->status;
   return 0;
+}
+
+// Block counters of the fused finalize: launches on one stream run one after another and each leaves its counter
+// at zero, so a small rotating pool is plenty. The NAME is only a handle for cudaGetSymbolAddress in host code.
+static __device__ unsigned int g_gn_tickets[256];
+constexpr int GN_TICKET_DEVICES = 64;
+static unsigned int* g_gn_ticket_ptr[GN_TICKET_DEVICES] = {nullptr};
+static std::atomic<unsigned int> g_gn_ticket_seq{0};
+static unsigned int* gn_ticket() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= GN_TICKET_DEVICES) return nullptr;
+  if (g_gn_ticket_ptr[dev] == nullptr) {
+    unsigned int* q = nullptr;
+    if (cudaGetSymbolAddress((void**)&q, g_gn_tickets) != cudaSuccess || q == nullptr) return nullptr;
+    g_gn_ticket_ptr[dev] = q;
+  }
+  return g_gn_ticket_ptr[dev] + (g_gn_ticket_seq.fetch_add(1u) % 256u);
 }
 
 static int apply_blocks(const GnParams& p) {
@@ -601,6 +663,7 @@ extern "C" int sb_gn_stats(const SbGnArgs* a, cudaStream_t stream) {
   GnParams p;
   int rc = gn_fill(a, p);
   if (rc) return rc;
+  if (p.fin != nullptr && (p.ticket = gn_ticket()) == nullptr) return SB_ERR_DRIVER;
   gn_stats_kernel<<<dim3(p.nsplit, p.N), GN_THREADS, 0, stream>>>(p);
   sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
@@ -619,6 +682,7 @@ extern "C" int sb_gn_bwd_partial(const SbGnArgs* a, cudaStream_t stream) {
   GnParams p;
   int rc = gn_fill(a, p);
   if (rc) return rc;
+  if (p.fin != nullptr && (p.ticket = gn_ticket()) == nullptr) return SB_ERR_DRIVER;
   gn_bwd_partial_kernel<<<dim3(p.nsplit, p.N), GN_THREADS, 0, stream>>>(p);
   sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
@@ -733,10 +797,10 @@ extern "C" int sb_gn_forward_noalloc(const void* x, void* y, const float* w, con
   a.parts[0] = part;
   a.n_parts = 1;
   a.nsplit = nsplit;
+  a.fin = fin;  // the statistics launch collapses its own partials (last block)
   int rc = sb_gn_stats(&a, stream);
   if (rc) return rc;
-  rc = sb_gn_stats_finalize(part, fin, N, G, nsplit, stream);
-  if (rc) return rc;
+  a.fin = nullptr;
   a.parts[0] = fin;
   a.nsplit = 1;
   return sb_gn_apply(&a, stream);

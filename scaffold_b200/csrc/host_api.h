@@ -159,6 +159,9 @@ typedef struct {
   unsigned wait_epoch;
   double wait_s;
   unsigned* status;
+  // sb_gn_stats / sb_gn_bwd_partial: when set, the last block of the launch also collapses the partials into
+  // fin ([N*G*3] resp. [N*C*2], the output of sb_gn_stats_finalize / sb_gn_bwd_finalize): one launch instead of two
+  float* fin;
 } SbGnArgs;
 
 // Stores `count` floats of `fin` into dst[r] for every r < world (peer pointers valid on this GPU),

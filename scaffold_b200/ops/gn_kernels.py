@@ -8,6 +8,7 @@ result equals the unsharded normalisation.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -46,6 +47,7 @@ class SbGnArgs(C.Structure):
         ("wait_epoch", C.c_uint),
         ("wait_s", C.c_double),
         ("status", C.c_void_p),
+        ("fin", C.c_void_p),
     ]
 
 
@@ -55,6 +57,11 @@ _lib.register("sb_gn_stats_finalize", [C.c_void_p, C.c_void_p, C.c_int, C.c_int,
 _lib.register("sb_gn_bwd_finalize", [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p], C.c_int)
 _lib.register("sb_gn_share", [C.c_void_p, C.c_longlong, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int,
                               C.c_uint, C.c_void_p], C.c_int)
+
+
+# SCAFFOLD_GN_FUSED_FINALIZE=0 collapses the partial statistics in a launch of its own (the A/B switch of the
+# last-block hand-over inside the statistics kernels)
+_FUSED_FINALIZE = os.environ.get("SCAFFOLD_GN_FUSED_FINALIZE", "1") != "0"
 
 
 def _base(x: torch.Tensor, w, b, groups: int, eps: float, relu: bool, shards: int, nsplit: int = 0) -> SbGnArgs:
@@ -90,11 +97,15 @@ def gn_stats(x, w, b, groups, eps, relu, part: Optional[torch.Tensor] = None,
     a.part = part.data_ptr()
     a.n_parts = 1
     a.parts[0] = part.data_ptr()
-    _lib.check(_lib.lib().sb_gn_stats(C.byref(a), _lib.stream_ptr()), "sb_gn_stats")
     if fin is None:
         fin = torch.empty(x.shape[0] * groups * 3, dtype=torch.float32, device=x.device)
-    _lib.check(_lib.lib().sb_gn_stats_finalize(part.data_ptr(), fin.data_ptr(), x.shape[0], groups, a.nsplit,
-                                               _lib.stream_ptr()), "sb_gn_stats_finalize")
+    fused = _FUSED_FINALIZE and x.shape[0] * groups <= 32
+    if fused:
+        a.fin = fin.data_ptr()  # the last block of the launch collapses the partials: no separate finalize launch
+    _lib.check(_lib.lib().sb_gn_stats(C.byref(a), _lib.stream_ptr()), "sb_gn_stats")
+    if not fused:
+        _lib.check(_lib.lib().sb_gn_stats_finalize(part.data_ptr(), fin.data_ptr(), x.shape[0], groups, a.nsplit,
+                                                   _lib.stream_ptr()), "sb_gn_stats_finalize")
     return fin
 
 
@@ -150,11 +161,17 @@ def gn_bwd_partial(dy, x, w, b, mean, rstd, groups, eps, relu, part: Optional[to
     a.part = part.data_ptr()
     a.n_parts = 1
     a.parts[0] = part.data_ptr()
-    _lib.check(_lib.lib().sb_gn_bwd_partial(C.byref(a), _lib.stream_ptr()), "sb_gn_bwd_partial")
     if fin is None:
         fin = torch.empty(x.shape[0] * x.shape[4] * 2, dtype=torch.float32, device=x.device)
-    _lib.check(_lib.lib().sb_gn_bwd_finalize(part.data_ptr(), fin.data_ptr(), x.shape[0], x.shape[4], a.nsplit,
-                                             _lib.stream_ptr()), "sb_gn_bwd_finalize")
+    # The hand-over to the last block pays only while that one block has a handful of outputs to collapse: N*C
+    # per-channel sums would make it a serial tail (measured: +1.6 ms per step), so they keep their own launch.
+    fused = _FUSED_FINALIZE and x.shape[0] * x.shape[4] <= 32
+    if fused:
+        a.fin = fin.data_ptr()
+    _lib.check(_lib.lib().sb_gn_bwd_partial(C.byref(a), _lib.stream_ptr()), "sb_gn_bwd_partial")
+    if not fused:
+        _lib.check(_lib.lib().sb_gn_bwd_finalize(part.data_ptr(), fin.data_ptr(), x.shape[0], x.shape[4], a.nsplit,
+                                                 _lib.stream_ptr()), "sb_gn_bwd_finalize")
     return fin
 
 
