@@ -186,14 +186,16 @@ def pool_case(op: str, channels: int, size: int, batch: int, library: bool = Tru
     nbuf = _copies(n * s ** 3 * c * 2)
     xs = _rot(nbuf, lambda: torch.randn(n, s, s, s, c, device=dev).to(torch.bfloat16))
     vol = n * s ** 3 * c * 2
+    # the pair the module runs: forward also writes one index byte per output element, backward reads gy + indices
     if op == "pool_fwd":
-        ours = lambda i: pk.maxpool2_fwd(xs[i % nbuf])
-        nbytes = vol + vol // 8
+        ours = lambda i: pk.maxpool2_fwd_idx(xs[i % nbuf])
+        nbytes = vol + vol // 8 + vol // 16
         lib = (lambda i: F.max_pool3d(xs[i % nbuf].permute(0, 4, 1, 2, 3), 2)) if library else None
     else:
-        ys = [pk.maxpool2_fwd(x) for x in xs]
-        gys = [torch.randn_like(y) for y in ys]
-        ours = lambda i: pk.maxpool2_bwd(gys[i % nbuf], xs[i % nbuf], ys[i % nbuf])
-        nbytes = 2 * vol + 2 * (vol // 8)
+        pairs = [pk.maxpool2_fwd_idx(x) for x in xs]
+        gys = [torch.randn_like(y) for y, _ in pairs]
+        shape = tuple(xs[0].shape)
+        ours = lambda i: pk.maxpool2_bwd_idx(gys[i % nbuf], pairs[i % nbuf][1], shape)
+        nbytes = vol + vol // 8 + vol // 16
         lib = None
     return Case(op, f"C={c} @{size}^3 n{batch}", ours, lib, bytes=float(nbytes))

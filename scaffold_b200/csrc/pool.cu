@@ -107,6 +107,94 @@ __global__ void __launch_bounds__(256) maxpool2_bwd_kernel(const __nv_bfloat16* 
   }
 }
 
+// Forward that also records, per output element, WHICH of its eight inputs is the maximum (one byte per channel,
+// eight channels = one 64-bit word per thread; first match in (kd,kh,kw) order, a NaN wins over numbers and the first
+// NaN over later ones: the rule of the kernels above). The backward pass below then needs neither x nor y: it reads
+// gy and the index words (3/16 of a volume) and writes gx, instead of reading a whole volume of x again.
+__global__ void __launch_bounds__(256) maxpool2_fwd_idx_kernel(const __nv_bfloat16* __restrict__ x,
+                                                               __nv_bfloat16* __restrict__ y,
+                                                               unsigned long long* __restrict__ idx, int N, int D,
+                                                               int H, int W, int C) {
+  const int OD = D / 2, OH = H / 2, OW = W / 2, C8 = C / 8;
+  const long long total = (long long)N * OD * OH * OW * C8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long t = i;
+    const int c8 = (int)(t % C8); t /= C8;
+    const int ow = (int)(t % OW); t /= OW;
+    const int oh = (int)(t % OH); t /= OH;
+    const int od = (int)(t % OD); t /= OD;
+    const int n = (int)t;
+    float m[8];
+    unsigned int bi[8];  // index k of channel j's maximum
+    uint4 raw[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int kd = k >> 2, kh = (k >> 1) & 1, kw = k & 1;
+      const long long v = (((long long)n * D + (2 * od + kd)) * H + (2 * oh + kh)) * W + (2 * ow + kw);
+      raw[k] = __ldg(reinterpret_cast<const uint4*>(x + v * C + c8 * 8));
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float f[8];
+      unpack8p(raw[k], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (k == 0) {
+          m[j] = f[j];
+          bi[j] = 0u;
+        } else if (m[j] == m[j] && (f[j] != f[j] || f[j] > m[j])) {  // keep a NaN; else take a NaN or a larger value
+          m[j] = f[j];
+          bi[j] = (unsigned int)k;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (m[j] != m[j]) m[j] = __int_as_float(0x7fc00000);
+    uint4 o;
+    o.x = pack_bf16x2(m[0], m[1]);
+    o.y = pack_bf16x2(m[2], m[3]);
+    o.z = pack_bf16x2(m[4], m[5]);
+    o.w = pack_bf16x2(m[6], m[7]);
+    *reinterpret_cast<uint4*>(y + i * 8) = o;
+    // byte j of the index word: channel j's winner
+    const unsigned int lo = bi[0] | (bi[1] << 8) | (bi[2] << 16) | (bi[3] << 24);
+    const unsigned int hi = bi[4] | (bi[5] << 8) | (bi[6] << 16) | (bi[7] << 24);
+    idx[i] = (unsigned long long)lo | ((unsigned long long)hi << 32);
+  }
+}
+
+__global__ void __launch_bounds__(256) maxpool2_bwd_idx_kernel(const __nv_bfloat16* __restrict__ gy,
+                                                               const unsigned long long* __restrict__ idx,
+                                                               __nv_bfloat16* __restrict__ gx, int N, int D, int H,
+                                                               int W, int C) {
+  const int OD = D / 2, OH = H / 2, OW = W / 2, C8 = C / 8;
+  const long long total = (long long)N * OD * OH * OW * C8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long t = i;
+    const int c8 = (int)(t % C8); t /= C8;
+    const int ow = (int)(t % OW); t /= OW;
+    const int oh = (int)(t % OH); t /= OH;
+    const int od = (int)(t % OD); t /= OD;
+    const int n = (int)t;
+    const uint4 rg = __ldg(reinterpret_cast<const uint4*>(gy + i * 8));
+    const unsigned long long which = __ldg(idx + i);
+    const unsigned short* gs = reinterpret_cast<const unsigned short*>(&rg);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int kd = k >> 2, kh = (k >> 1) & 1, kw = k & 1;
+      const long long v = (((long long)n * D + (2 * od + kd)) * H + (2 * oh + kh)) * W + (2 * ow + kw);
+      uint4 o;
+      unsigned short* os = reinterpret_cast<unsigned short*>(&o);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) os[j] = ((which >> (8 * j)) & 0xffull) == (unsigned long long)k ? gs[j] : (unsigned short)0;
+      *reinterpret_cast<uint4*>(gx + v * C + c8 * 8) = o;
+    }
+  }
+}
+
 // zero the planes a floor-mode pool never reads (odd extents)
 __global__ void maxpool2_bwd_tail_kernel(__nv_bfloat16* gx, int N, int D, int H, int W, int C) {
   const long long total = (long long)N * D * H * W;
@@ -142,6 +230,33 @@ extern "C" int sb_maxpool2_bwd(const void* gy, const void* x, const void* y, voi
   const long long total = (long long)N * (D / 2) * (H / 2) * (W / 2) * (C / 8);
   maxpool2_bwd_kernel<<<pool_grid(total), 256, 0, stream>>>((const __nv_bfloat16*)gy, (const __nv_bfloat16*)x,
                                                             (const __nv_bfloat16*)y, (__nv_bfloat16*)gx, N, D, H, W, C);
+  sb_count_launch(1);
+  if ((D | H | W) & 1) {
+    maxpool2_bwd_tail_kernel<<<pool_grid((long long)N * D * H * W), 256, 0, stream>>>((__nv_bfloat16*)gx, N, D, H, W, C);
+    sb_count_launch(1);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
+// Forward that also writes the index words (N * D/2 * H/2 * W/2 * C/8 of them) for sb_maxpool2_bwd_idx.
+extern "C" int sb_maxpool2_fwd_idx(const void* x, void* y, void* idx, int N, int D, int H, int W, int C,
+                                   cudaStream_t stream) {
+  if (C % 8 != 0 || D < 2 || H < 2 || W < 2 || idx == nullptr) return SB_ERR_SHAPE;
+  const long long total = (long long)N * (D / 2) * (H / 2) * (W / 2) * (C / 8);
+  maxpool2_fwd_idx_kernel<<<pool_grid(total), 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y,
+                                                                (unsigned long long*)idx, N, D, H, W, C);
+  sb_count_launch(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
+}
+
+// Backward from the index words: reads gy and idx only.
+extern "C" int sb_maxpool2_bwd_idx(const void* gy, const void* idx, void* gx, int N, int D, int H, int W, int C,
+                                   cudaStream_t stream) {
+  if (C % 8 != 0 || D < 2 || H < 2 || W < 2 || idx == nullptr) return SB_ERR_SHAPE;
+  const long long total = (long long)N * (D / 2) * (H / 2) * (W / 2) * (C / 8);
+  maxpool2_bwd_idx_kernel<<<pool_grid(total), 256, 0, stream>>>((const __nv_bfloat16*)gy,
+                                                                (const unsigned long long*)idx, (__nv_bfloat16*)gx, N,
+                                                                D, H, W, C);
   sb_count_launch(1);
   if ((D | H | W) & 1) {
     maxpool2_bwd_tail_kernel<<<pool_grid((long long)N * D * H * W), 256, 0, stream>>>((__nv_bfloat16*)gx, N, D, H, W, C);

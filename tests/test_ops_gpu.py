@@ -36,6 +36,35 @@ def test_maxpool_odd_extent_tail_is_zeroed():
     assert gx[:, 4].abs().sum().item() == 0 and gx[:, :, :, 6].abs().sum().item() == 0
 
 
+@pytest.mark.parametrize("shape", [(2, 8, 6, 10, 32), (1, 5, 4, 7, 16), (2, 16, 16, 16, 128)])
+def test_maxpool_index_variant_equals_the_recomputing_pair(shape):
+    """The module's pool keeps one index byte per output element instead of x and y; output and input gradient
+    must be the bits of the kernels that recompute the winner, ties, signed zeros and NaNs included."""
+    from scaffold_b200.ops import pool_kernels as pk
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(shape, generator=g, device="cuda").to(torch.bfloat16)
+    x[0, 0, 0, 0, 0] = 0.0
+    x[0, 0, 0, 1, 0] = -0.0
+    x[0, 0, 1, 0, 0] = 0.0
+    x[0, 1, 1, 1, 0] = -0.0
+    x[0, :2, :2, :2, 1] = 1.5                      # an eight-way tie
+    x[0, 0, 1, 1, 2] = float("nan")                # one NaN in a window
+    x[0, 1, 0, 0, 3] = float("nan")
+    x[0, 1, 1, 0, 3] = float("nan")                # two NaNs: the first one takes the gradient
+    y0 = pk.maxpool2_fwd(x)
+    y1, idx = pk.maxpool2_fwd_idx(x)
+    assert torch.equal(y0.view(torch.int16), y1.view(torch.int16))
+    gy = torch.randn(y0.shape, generator=g, device="cuda").to(torch.bfloat16)
+    gx0 = pk.maxpool2_bwd(gy, x, y0)
+    gx1 = pk.maxpool2_bwd_idx(gy, idx, x.shape)
+    torch.cuda.synchronize()
+    assert torch.equal(gx0.view(torch.int16), gx1.view(torch.int16))
+    # through autograd (the module path)
+    xv = x.clone().requires_grad_(True)
+    pk.MaxPool2Fn.apply(xv).backward(gy)
+    assert torch.equal(xv.grad.view(torch.int16), gx0.view(torch.int16))
+
+
 @pytest.mark.parametrize("n_classes,weights", [(6, True), (9, False), (17, True)])
 def test_fused_loss_matches_reference(n_classes, weights):
     from scaffold_b200.ops import loss as L
