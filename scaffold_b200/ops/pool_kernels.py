@@ -74,7 +74,8 @@ class MaxPool2Fn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, gy):
-        if len(ctx.saved_tensors) == 1:
-            return maxpool2_bwd_idx(gy.contiguous(), ctx.saved_tensors[0], ctx.in_shape)
-        x, y = ctx.saved_tensors
+        saved = ctx.saved_tensors  # read once: activation checkpointing unpacks on access
+        if len(saved) == 1:
+            return maxpool2_bwd_idx(gy.contiguous(), saved[0], ctx.in_shape)
+        x, y = saved
         return maxpool2_bwd(gy.contiguous(), x, y)
