@@ -262,6 +262,8 @@ __global__ void wgrad_reduce_kernel(const ReduceParams p) {
 // It reads 27 runs of CT consecutive floats per split as 16-byte vectors, four in flight per thread (summed in
 // split order), and writes the CT x 27 floats that are contiguous in dw[co][ci][tap] as 16-byte vectors.
 constexpr int RT_MAX_CT = 128;
+// MANY: the layer has at least four splits (small weights, few blocks): four splits per trip, 16 loads in flight.
+template <bool MANY>
 __global__ void __launch_bounds__(256) wgrad_reduce_t_kernel(const ReduceParams p, const int CT) {
   __shared__ float t[27][RT_MAX_CT + 1];
   const int co = blockIdx.y, ci0 = blockIdx.x * CT;
@@ -277,18 +279,56 @@ __global__ void __launch_bounds__(256) wgrad_reduce_t_kernel(const ReduceParams 
       c4[u] = (e - tap[u] * v_per_run) * 4;
       acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    for (int sp = 0; sp < p.splits; ++sp) {
-      float4 v[4];
+    if constexpr (MANY) {
+      // Layers with small weights have many splits and few blocks: four splits per trip keep 16 loads in flight
+      // per thread; the sums are still taken in split order.
+      const float* base[4];
+      bool live[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (e0 + u * 256 < nvec)
-          v[u] = __ldcs(reinterpret_cast<const float4*>(p.ws + (size_t)sp * slice +
-                                                        ((size_t)tap[u] * p.Mtot + co) * p.Ntot + ci0 + c4[u]));
+        live[u] = e0 + u * 256 < nvec;
+        base[u] = p.ws + ((size_t)tap[u] * p.Mtot + co) * p.Ntot + ci0 + c4[u];
       }
+      int sp = 0;
+      for (; sp + 4 <= p.splits; sp += 4) {
+        float4 v[4][4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w;
+        for (int k = 0; k < 4; ++k)
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            v[k][u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (live[u]) v[k][u] = __ldcs(reinterpret_cast<const float4*>(base[u] + (size_t)(sp + k) * slice));
+          }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            acc[u].x += v[k][u].x; acc[u].y += v[k][u].y; acc[u].z += v[k][u].z; acc[u].w += v[k][u].w;
+          }
+      }
+      for (; sp < p.splits; ++sp) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (live[u]) {
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(base[u] + (size_t)sp * slice));
+            acc[u].x += v.x; acc[u].y += v.y; acc[u].z += v.z; acc[u].w += v.w;
+          }
+        }
+      }
+    } else {
+      for (int sp = 0; sp < p.splits; ++sp) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (e0 + u * 256 < nvec)
+            v[u] = __ldcs(reinterpret_cast<const float4*>(p.ws + (size_t)sp * slice +
+                                                          ((size_t)tap[u] * p.Mtot + co) * p.Ntot + ci0 + c4[u]));
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w;
+        }
       }
     }
 #pragma unroll
@@ -533,8 +573,11 @@ static int run_reduce(const SbWgradArgs* a, ReduceParams& r, cudaStream_t stream
   const long long blocks = (r.total + threads - 1) / threads;
   if (r.mode == 0 && r.taps == 27 && r.cin % 32 == 0 && r.cout <= 65535 && r.Ntot % 4 == 0 &&
       (reinterpret_cast<uintptr_t>(r.dw) & 15) == 0 && (reinterpret_cast<uintptr_t>(r.ws) & 15) == 0) {
-    const int ct = r.cin % 128 == 0 ? 128 : (r.cin % 64 == 0 ? 64 : 32);
-    wgrad_reduce_t_kernel<<<dim3(r.cin / ct, r.cout), threads, 0, stream>>>(r, ct);
+    // the widest input-channel tile that still leaves about two blocks per SM (small weights: narrower tiles)
+    int ct = r.cin % 128 == 0 ? 128 : (r.cin % 64 == 0 ? 64 : 32);
+    while (ct > 32 && (long long)(r.cin / ct) * r.cout < 296) ct /= 2;
+    if (r.splits >= 4) wgrad_reduce_t_kernel<true><<<dim3(r.cin / ct, r.cout), threads, 0, stream>>>(r, ct);
+    else wgrad_reduce_t_kernel<false><<<dim3(r.cin / ct, r.cout), threads, 0, stream>>>(r, ct);
   } else
     wgrad_reduce_kernel<<<(unsigned)blocks, threads, 0, stream>>>(r);
   sb_count_launch(1);
