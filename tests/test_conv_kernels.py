@@ -72,6 +72,9 @@ FWD_CASES = [
     (1, 2, 16, 16, [64], 9, 1, 0),
     (1, 32, 32, 32, [64], 64, 3, 0),
     (1, 8, 8, 8, [512], 128, 3, 0),
+    (2, 8, 16, 16, [9], 64, 1, 0),       # k = 1 from <= 16 channels (the head's backward-data shape)
+    (2, 8, 16, 16, [9], 64, 1, 1),
+    (1, 3, 5, 7, [16], 72, 1, 0),        # ragged voxel count, 80 padded outputs
 ]
 
 
