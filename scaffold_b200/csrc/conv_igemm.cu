@@ -424,6 +424,7 @@ using namespace sb;
 namespace sb {
 int conv_plane_launch(const SbConvArgs* a, cudaStream_t stream);
 int conv_plane2_launch(const SbConvArgs* a, cudaStream_t stream);
+int conv_plane2_gn_splits(const SbConvArgs* a);
 int conv_plane3_launch(const SbConvArgs* a, cudaStream_t stream);
 int conv_plane3_gn_splits(const SbConvArgs* a);
 int conv_small_launch(const SbConvArgs* a, cudaStream_t stream);
@@ -437,8 +438,15 @@ extern "C" long long sb_conv_fwd_workspace(const SbConvArgs* a) {
   return automatic(a) ? conv_small_workspace(a) : 0;
 }
 
+static bool pair_first(const SbConvArgs* a) { return a->force_plain == 0 && a->wpack_kd == nullptr; }
+
 extern "C" int sb_conv_gn_splits(const SbConvArgs* a) {
-  return automatic(a) ? conv_plane3_gn_splits(a) : 0;
+  if (!automatic(a)) return 0;
+  if (pair_first(a)) {
+    const int s2 = conv_plane2_gn_splits(a);
+    if (s2 > 0) return s2;
+  }
+  return conv_plane3_gn_splits(a);
 }
 
 // force_plain: 0 = automatic (8 x 8 plane kernel; the two-SM pair kernel for wide outputs given tap-ordered
@@ -449,7 +457,8 @@ extern "C" int sb_conv_fwd(const SbConvArgs* a, cudaStream_t stream) {
   if (automatic(a)) {
     const int sm = conv_small_launch(a, stream);
     if (sm >= 0) return sm;
-    if (a->force_plain == 0 && a->wpack_kd == nullptr && a->gn_part == nullptr) {
+    // with a partial-statistics buffer only when the pair kernel is the one that sized it (sb_conv_gn_splits)
+    if (pair_first(a) && (a->gn_part == nullptr || conv_plane2_gn_splits(a) > 0)) {
       const int p2 = conv_plane2_launch(a, stream);
       if (p2 >= 0) return p2;
     }

@@ -60,6 +60,9 @@ struct Plane2Params {
   int width0, width1, ld0, ld1;
   const float* bias;
   uint32_t* status;
+  // optional GroupNorm partials of the output: [N][gn_splits][gn_groups][3] (count, mean, M2), one per epilogue warp
+  float* gn_part;
+  int gn_groups, gn_cg, gn_splits;
 };
 
 struct Job2 {
@@ -187,7 +190,9 @@ __device__ __forceinline__ void tc2_mma_bf16_pred(uint32_t tmem_d, uint32_t a_lo
       : "memory");
 }
 
-template <int TD>
+// STATS: the epilogue also leaves GroupNorm partial statistics of what it stores (forward passes that feed a
+// GroupNorm; groups of 16 channels or more, i.e. whole halves of a 32-column TMEM chunk).
+template <int TD, bool STATS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(224, 1)
 conv_plane2_kernel(const __grid_constant__ Plane2Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -199,6 +204,7 @@ conv_plane2_kernel(const __grid_constant__ Plane2Params p) {
   __shared__ uint64_t tempty[8];
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t abort_s;
+  __shared__ float gn_acc[4][16][2];  // per epilogue warp: (sum, sum of squares) of up to 16 groups of this job
   volatile uint32_t* abort_flag = &abort_s;
 
   const int warp = threadIdx.x >> 5;
@@ -405,6 +411,11 @@ conv_plane2_kernel(const __grid_constant__ Plane2Params p) {
       tc_fence_after();
       const Job2 jc = decode_job2(p, pj, (int)rank);
       const int h = jc.h0 + rh, w = jc.w0 + rw;
+      float gcnt = 0.f;  // valid voxels of this warp's 32 rows over the job's planes (lane 0 keeps the total)
+      if (STATS) {
+        if (lane < 16) { gn_acc[q][lane][0] = 0.f; gn_acc[q][lane][1] = 0.f; }
+        __syncwarp();
+      }
       for (int t = 0; t < TD; ++t) {
         const int d = jc.d0 + t;
         const bool valid = h < p.H && w < p.W && d < p.D && jc.n < p.N;
@@ -419,10 +430,12 @@ conv_plane2_kernel(const __grid_constant__ Plane2Params p) {
         const uint32_t acc_i = buf * TD + t;
         const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + acc_i * p.BN;
         const int nchunk = p.BN / 32;
+        if (STATS) gcnt += (float)__popc(__ballot_sync(0xffffffffu, valid));
         for (int ch = 0; ch < nchunk; ++ch) {
           uint32_t v[32];
           tmem_ld_32x32(tbase + ch * 32, v);
           tmem_ld_wait();
+          float st[2][2] = {{0.f, 0.f}, {0.f, 0.f}};  // [half of the chunk][sum, sum of squares], as stored
           if (valid) {
 #pragma unroll
             for (int g = 0; g < 2; ++g) {
@@ -453,6 +466,35 @@ conv_plane2_kernel(const __grid_constant__ Plane2Params p) {
                 hi.z = pack_bf16x2(f[12], f[13]);
                 hi.w = pack_bf16x2(f[14], f[15]);
                 st_global_v8(dst, lo, hi);
+                if (STATS) {
+                  // the values as stored (bf16-rounded): the statistics describe the tensor the next pass reads
+                  const uint32_t w8[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    const float a0 = __uint_as_float(w8[e] << 16), a1 = __uint_as_float(w8[e] & 0xffff0000u);
+                    st[g][0] += a0 + a1;
+                    st[g][1] += a0 * a0 + a1 * a1;
+                  }
+                }
+              }
+            }
+          }
+          if (STATS) {
+            // warp sums of the two 16-channel halves; lane 0 adds them to the job's group accumulators (fixed order)
+#pragma unroll
+            for (int o2 = 16; o2 > 0; o2 >>= 1) {
+#pragma unroll
+              for (int g = 0; g < 2; ++g) {
+                st[g][0] += __shfl_xor_sync(0xffffffffu, st[g][0], o2);
+                st[g][1] += __shfl_xor_sync(0xffffffffu, st[g][1], o2);
+              }
+            }
+            if (lane == 0) {
+#pragma unroll
+              for (int g = 0; g < 2; ++g) {
+                const int gl = (ch * 32 + g * 16) / p.gn_cg;  // group of this half inside the job's channel tile
+                gn_acc[q][gl][0] += st[g][0];
+                gn_acc[q][gl][1] += st[g][1];
               }
             }
           }
@@ -460,6 +502,22 @@ conv_plane2_kernel(const __grid_constant__ Plane2Params p) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_remote(map_to_rank(smem_u32(&tempty[acc_i]), 0));
+      }
+      if (STATS) {
+        __syncwarp();
+        const int groups_here = p.BN / p.gn_cg;
+        const float n_vox = __shfl_sync(0xffffffffu, gcnt, 0);
+        if (lane < groups_here && jc.n < p.N) {
+          const float s1 = gn_acc[q][lane][0], s2 = gn_acc[q][lane][1];
+          const float n_el = n_vox * (float)p.gn_cg;
+          const float mean = n_el > 0.f ? s1 / n_el : 0.f;
+          const float m2 = n_el > 0.f ? fmaxf(s2 - s1 * mean, 0.f) : 0.f;
+          const int sj = ((jc.d0 / TD * p.tiles_h + jc.h0 / 8) * p.tiles_w + jc.w0 / 16) * 4 + q;
+          const int g_glob = jc.co0 / p.gn_cg + lane;
+          float* dst = p.gn_part + (((long long)jc.n * p.gn_splits + sj) * p.gn_groups + g_glob) * 3;
+          dst[0] = n_el; dst[1] = mean; dst[2] = m2;
+        }
+        __syncwarp();  // gn_acc[q] is cleared by this warp at its next job
       }
     }
   }
@@ -488,9 +546,10 @@ static int p2_setup() {
   int lim = 0, sms = 0;
   cudaDeviceGetAttribute(&lim, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const void* fns[3] = {(const void*)conv_plane2_kernel<1>, (const void*)conv_plane2_kernel<2>,
-                        (const void*)conv_plane2_kernel<4>};
-  for (int i = 0; i < 3; ++i)
+  const void* fns[6] = {(const void*)conv_plane2_kernel<1, false>, (const void*)conv_plane2_kernel<2, false>,
+                        (const void*)conv_plane2_kernel<4, false>, (const void*)conv_plane2_kernel<1, true>,
+                        (const void*)conv_plane2_kernel<2, true>, (const void*)conv_plane2_kernel<4, true>};
+  for (int i = 0; i < 6; ++i)
     if (cudaFuncSetAttribute(fns[i], cudaFuncAttributeMaxDynamicSharedMemorySize, lim - 2048) != cudaSuccess)
       return SB_ERR_DRIVER;
   g_p2_smem = lim - 2048;
@@ -509,7 +568,7 @@ static int p2_setup() {
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, conv_plane2_kernel<2>, &cfg) == cudaSuccess && n > 0 && n < sms / 2)
+  if (cudaOccupancyMaxActiveClusters(&n, conv_plane2_kernel<2, true>, &cfg) == cudaSuccess && n > 0 && n < sms / 2)
     g_p2_clusters = n;
   else
     g_p2_clusters = sms / 2;
@@ -563,6 +622,30 @@ static bool p2_choose(const SbConvArgs* a, int bn_max, int cblks, int clusters, 
     }
   }
   return found;
+}
+
+// GroupNorm statistics from the epilogue: one destination, no slab outputs, groups of whole 16-channel halves of a
+// TMEM chunk that do not straddle channel tiles, at most 16 groups per tile.
+static bool p2_gn_ok(const SbConvArgs* a, int bn) {
+  if (a->gn_groups < 1 || a->dst[1] != nullptr || a->slab_out[0] != nullptr) return false;
+  if (a->dst_c[0] != a->cout_pad || a->cout_pad % a->gn_groups != 0) return false;
+  const int cg = a->cout_pad / a->gn_groups;
+  return cg % 16 == 0 && cg <= bn && bn % cg == 0 && bn / cg <= 16;
+}
+
+// Partials per sample the pair kernel would write for this call (0: it will not produce statistics).
+int conv_plane2_gn_splits(const SbConvArgs* a) {
+  const int bn_max = conv_plane2_bn(a);
+  if (bn_max == 0 || p2_setup() != 0) return 0;
+  const int cblks = (a->src_c[0] + a->src_c[1]) / P2_BK;
+  const int a_tx = P2_RH * P2_RW * P2_ROWB;
+  const int a_slot_bytes = ((a_tx + 1023) / 1024) * 1024;
+  int bn = 0, td = 1;
+  if (!p2_choose(a, bn_max, cblks, g_p2_clusters, a_slot_bytes, g_p2_smem - 1024, &bn, &td)) return 0;
+  if (!p2_gn_ok(a, bn)) return 0;
+  // the launcher's own refusals (it then falls back to the single-CTA kernels, which get no partial buffer)
+  if (a->dst_c[0] % 16 || a->dst_ld[0] % 16 || (reinterpret_cast<uintptr_t>(a->dst[0]) & 31)) return 0;
+  return cdiv_p2(a->D, td) * cdiv_p2(a->H, 8) * cdiv_p2(a->W, 16) * 4;
 }
 
 // Returns -1 when the shape is not eligible (the caller then uses the single-CTA kernels).
@@ -667,9 +750,20 @@ int conv_plane2_launch(const SbConvArgs* a, cudaStream_t stream) {
   const int use = p.num_pair_jobs < clusters ? p.num_pair_jobs : clusters;
   const int grid = 2 * use;
   const size_t smem = (size_t)p.a_slots * p.a_slot_bytes + (size_t)p.b_slots * p.b_slot_bytes + 1024;
-  if (td == 4) conv_plane2_kernel<4><<<grid, 224, smem, stream>>>(p);
-  else if (td == 2) conv_plane2_kernel<2><<<grid, 224, smem, stream>>>(p);
-  else conv_plane2_kernel<1><<<grid, 224, smem, stream>>>(p);
+  if (a->gn_part != nullptr) {
+    if (!p2_gn_ok(a, p.BN)) return SB_ERR_SHAPE;
+    p.gn_part = a->gn_part;
+    p.gn_groups = a->gn_groups;
+    p.gn_cg = a->cout_pad / a->gn_groups;
+    p.gn_splits = p.groups_d * p.tiles_h * p.tiles_w * 4;
+    if (td == 4) conv_plane2_kernel<4, true><<<grid, 224, smem, stream>>>(p);
+    else if (td == 2) conv_plane2_kernel<2, true><<<grid, 224, smem, stream>>>(p);
+    else conv_plane2_kernel<1, true><<<grid, 224, smem, stream>>>(p);
+  } else {
+    if (td == 4) conv_plane2_kernel<4, false><<<grid, 224, smem, stream>>>(p);
+    else if (td == 2) conv_plane2_kernel<2, false><<<grid, 224, smem, stream>>>(p);
+    else conv_plane2_kernel<1, false><<<grid, 224, smem, stream>>>(p);
+  }
   sb_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? 0 : SB_ERR_LAUNCH;
 }

@@ -9,6 +9,7 @@ the loader produced. The reference moves each batch synchronously at the top of 
 """
 from __future__ import annotations
 
+import time
 from typing import Any, Iterable, Iterator, List
 
 import torch
@@ -44,24 +45,36 @@ class DevicePrefetcher:
     def __init__(self, batches: Iterable, device):
         self.batches = batches
         self.device = torch.device(device)
+        self.wait_s = 0.0  # host time spent waiting for the wrapped loader to hand over a batch
 
     def __len__(self):
         return len(self.batches)
 
     def __iter__(self) -> Iterator:
         if self.device.type != "cuda":
-            yield from self.batches
-            return
+            it = iter(self.batches)
+            while True:
+                t0 = time.perf_counter()
+                try:
+                    batch = next(it)
+                except StopIteration:
+                    return
+                finally:
+                    self.wait_s += time.perf_counter() - t0
+                yield batch
         copy_stream = torch.cuda.Stream(device=self.device)
         it = iter(self.batches)
         slots: List[List[torch.Tensor]] = [[], []]
         free_ev = [None, None]  # recorded on the compute stream when the consumer came back for the next batch
 
         def load(k: int):
+            t0 = time.perf_counter()
             try:
                 host = next(it)
             except StopIteration:
                 return None
+            finally:
+                self.wait_s += time.perf_counter() - t0
             src: List[torch.Tensor] = []
             spec = _flatten(host, src)
             bufs = slots[k]

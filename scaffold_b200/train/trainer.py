@@ -315,7 +315,8 @@ class Trainer:
                 n_samples, steps, events = 0, 0, []
                 full_batches = self.n_train_local() // int(cfg.local_batch_size)
                 begin_code_region("batch_loop")
-                for bi, batch in enumerate(DevicePrefetcher(self.train_loader, self.device)):
+                prefetch = DevicePrefetcher(self.train_loader, self.device)
+                for bi, batch in enumerate(prefetch):
                     timed = self.device.type == "cuda" and bi < full_batches
                     if timed:
                         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -343,6 +344,7 @@ class Trainer:
                 epoch_loss_total = info[0].item()
                 overall_loss = epoch_loss_total / g_samples
                 train_dice = info[1].item() / g_samples
+                t_train = time.time() - t0  # the .item() above waited for the last step
 
                 d_sum, v_loss_epoch, _, _, n_val = evaluate(self.engine, self.val_loader, progress=self.world_rank == 0)
                 vinfo = torch.tensor([d_sum, v_loss_epoch, float(n_val)], device=self.device, dtype=torch.float32)
@@ -374,6 +376,9 @@ class Trainer:
                              f"Mvoxel/s)." if mb else "")
                     self.log.info("Epoch %s completed in %.6f seconds. Total train time so far: %.6f seconds.%s",
                                   epoch, duration, time.time() - start, extra)
+                    self.log.info("Epoch %s phases: training %.3f s (of which the host waited %.3f s for the data "
+                                  "loader), validation %.3f s.", epoch, t_train, prefetch.wait_s,
+                                  duration - t_train)
                 with region("checkpoint"):
                     if cfg.checkpoint_interval > 0 and epoch % cfg.checkpoint_interval == 0:
                         self._save(epoch, val_loss_avg, val_score)

@@ -166,8 +166,12 @@ def test_kernel_selection_report_lists_every_layer():
     assert "weight-grad" in text and "halo_exchange_effective: none" in text
 
 
+# the last five run the two-SM pair kernel (tile widths 128 and 256, groups of 16 to 128 channels, ragged planes)
 @pytest.mark.parametrize("cin,cout,dims,groups", [(64, 64, (8, 24, 40), 8), (32, 128, (5, 16, 16), 8),
-                                                  (64, 32, (4, 9, 17), 8), (64, 64, (2, 8, 16), 4)],
+                                                  (64, 32, (4, 9, 17), 8), (64, 64, (2, 8, 16), 4),
+                                                  (64, 128, (6, 16, 32), 8), (128, 256, (5, 16, 16), 8),
+                                                  (64, 512, (4, 8, 16), 8), (64, 1024, (2, 8, 16), 8),
+                                                  (64, 128, (5, 12, 20), 4)],
                          ids=lambda v: str(v))
 def test_groupnorm_statistics_from_the_convolution_epilogue_match_the_statistics_pass(cin, cout, dims, groups):
     from scaffold_b200.ops import _lib, conv_kernels as ck, gn_kernels as gk
