@@ -38,6 +38,7 @@ BENCHMARK_FLAGS = {
     "--unet-base-width": ("unet_base_width", int), "--gn-stats": ("gn_stats", str),
     "--grad-allreduce": ("grad_allreduce", str), "--halo-exchange": ("halo_exchange", str),
     "--grad-overlap": ("grad_overlap", int), "--allow-fallback": ("allow_fallback", int),
+    "--val-cache-gb": ("val_cache_gb", float),
 }
 GENERATE_FLAGS = {
     "--datagen-batch-size": ("datagen_batch_size", int), "--problem-scale": ("problem_scale", int),

@@ -23,6 +23,12 @@ MAX_SEED = 2**32 - 1
 _REQUIRED = object()
 
 
+def require_nonneg_number(name: str, value: Any) -> float:
+    if isinstance(value, bool) or not isinstance(value, (int, float)) or not (value >= 0):
+        raise ValueError(f"{name} must be a non-negative number; got {value!r}")
+    return float(value)
+
+
 def require_positive_int(name: str, value: Any) -> int:
     if isinstance(value, bool) or not isinstance(value, int) or value < 1:
         raise ValueError(f"{name} must be a positive integer; got {value!r}")
@@ -135,6 +141,7 @@ SCHEMA: List[Key] = [
     Key("grad_overlap", True, conv=_flag),
     Key("halo_exchange", "fused", conv=_choice("fused", "nccl")),
     Key("allow_fallback", False, conv=_flag),
+    Key("val_cache_gb", 16.0, scalar=True, conv=require_nonneg_number),  # GiB of device memory for the validation set
     Key("point_num_override", None, scalar=True),
     Key("datagen_device", "auto", conv=_choice("auto", "cpu", "cuda")),
 ]

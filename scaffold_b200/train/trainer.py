@@ -148,6 +148,10 @@ class Trainer:
         self.train_loader = DataLoader(self.train_set, batch_size=bs, sampler=self.train_sampler, drop_last=False,
                                        **common)
         self.val_loader = DataLoader(self.val_set, batch_size=bs, sampler=self.val_sampler, drop_last=False, **common)
+        # the validation set is the same every epoch: after the first pass it is replayed from device memory
+        from ..data.device_cache import CachedEvalLoader
+        budget = int(float(getattr(cfg, "val_cache_gb", 0.0) or 0.0) * 2 ** 30)
+        self.val_batches = CachedEvalLoader(self.val_loader, self.device, budget)
         self.global_batch = bs * replicas
         adiak_value("global_batch_size", self.global_batch)
 
@@ -346,7 +350,7 @@ class Trainer:
                 train_dice = info[1].item() / g_samples
                 t_train = time.time() - t0  # the .item() above waited for the last step
 
-                d_sum, v_loss_epoch, _, _, n_val = evaluate(self.engine, self.val_loader, progress=self.world_rank == 0)
+                d_sum, v_loss_epoch, _, _, n_val = evaluate(self.engine, self.val_batches, progress=self.world_rank == 0)
                 vinfo = torch.tensor([d_sum, v_loss_epoch, float(n_val)], device=self.device, dtype=torch.float32)
                 self._all_reduce_data_parallel(vinfo)
                 g_val = max(vinfo[2].item(), 1.0)
