@@ -100,6 +100,29 @@ def compute_ce_class_weights(train_set, n_categories: int, device, sample_fracti
     return weights
 
 
+class PrimedLoader:
+    """Iterable over a DataLoader whose next iterator can be created ahead of time.
+
+    ``prime()`` builds the iterator now, so the workers start loading the next epoch's first batches while the
+    caller does something else (the validation pass); the following ``iter()`` hands that iterator out. Without it
+    every epoch begins with the latency of one sample load (about 80 ms for a 128^3 volume), which is a tenth of an
+    epoch once four replicas share the training set."""
+
+    def __init__(self, loader):
+        self.loader = loader
+        self._it = None
+
+    def __len__(self):
+        return len(self.loader)
+
+    def prime(self) -> None:
+        self._it = iter(self.loader)
+
+    def __iter__(self):
+        it, self._it = self._it, None
+        return it if it is not None else iter(self.loader)
+
+
 def _collate(batch):
     return {"image": torch.stack([b["image"] for b in batch]), "mask": torch.stack([b["mask"] for b in batch])}
 
@@ -152,6 +175,7 @@ class Trainer:
         from ..data.device_cache import CachedEvalLoader
         budget = int(float(getattr(cfg, "val_cache_gb", 0.0) or 0.0) * 2 ** 30)
         self.val_batches = CachedEvalLoader(self.val_loader, self.device, budget)
+        self.train_batches = PrimedLoader(self.train_loader)
         self.global_batch = bs * replicas
         adiak_value("global_batch_size", self.global_batch)
 
@@ -319,7 +343,7 @@ class Trainer:
                 n_samples, steps, events = 0, 0, []
                 full_batches = self.n_train_local() // int(cfg.local_batch_size)
                 begin_code_region("batch_loop")
-                prefetch = DevicePrefetcher(self.train_loader, self.device)
+                prefetch = DevicePrefetcher(self.train_batches, self.device)
                 for bi, batch in enumerate(prefetch):
                     timed = self.device.type == "cuda" and bi < full_batches
                     if timed:
@@ -349,6 +373,9 @@ class Trainer:
                 overall_loss = epoch_loss_total / g_samples
                 train_dice = info[1].item() / g_samples
                 t_train = time.time() - t0  # the .item() above waited for the last step
+                # the next epoch's first batches load while validation runs
+                self.train_sampler.set_epoch(epoch + 1)
+                self.train_batches.prime()
 
                 d_sum, v_loss_epoch, _, _, n_val = evaluate(self.engine, self.val_batches, progress=self.world_rank == 0)
                 vinfo = torch.tensor([d_sum, v_loss_epoch, float(n_val)], device=self.device, dtype=torch.float32)

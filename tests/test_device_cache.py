@@ -74,3 +74,27 @@ def test_second_pass_replays_device_copies_and_the_metric_does_not_change():
     list(small)
     list(small)
     assert not small.resident and src.walks == 3
+
+
+def test_primed_loader_hands_out_the_iterator_it_created_ahead_of_time():
+    from scaffold_b200.train.trainer import PrimedLoader
+
+    class Counting:
+        def __init__(self):
+            self.made = 0
+
+        def __len__(self):
+            return 3
+
+        def __iter__(self):
+            self.made += 1
+            return iter(range(3))
+
+    src = Counting()
+    p = PrimedLoader(src)
+    assert list(p) == [0, 1, 2] and src.made == 1      # not primed: a fresh iterator
+    p.prime()
+    assert src.made == 2                               # created now, ahead of its use
+    assert list(p) == [0, 1, 2] and src.made == 2      # ... and handed out once
+    assert list(p) == [0, 1, 2] and src.made == 3
+    assert len(p) == 3
