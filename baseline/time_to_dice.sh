@@ -8,7 +8,7 @@
 #    that step 1 generated, same batch size, seeds and schedule.
 # Both write train_stats.csv; the summary lines land in <out_dir>/summary.txt.
 set -euo pipefail
-GPUS="${1:-1}"; SCALE="${2:-7}"; NINST="${3:-32}"; BATCH="${4:-1}"; OUT="${5:-gpurun_out/ttd}"; MAXEP="${6:-120}"
+GPUS="${1:-1}"; SCALE="${2:-7}"; NINST="${3:-32}"; BATCH="${4:-1}"; OUT="${5:-out/ttd}"; MAXEP="${6:-120}"
 REPO="$(cd "$(dirname "${BASH_SOURCE[0]}")/.." && pwd)"
 cd "$REPO"
 WORK="${WORK:-/tmp/scaffold_ttd}"

@@ -6,7 +6,7 @@ shape occurs in a step, FLOPs, bytes, roofline, the kernel each direction routes
 library's measured milliseconds per call, and the per-step totals. The committed fixture
 ``data/scaffold_corpus_scale7_b200.json`` is what tests and "which layers matter" decisions read.
 
-    python -m scaffold_b200.analysis.corpus --sweep-json gpurun_out/sweep.json \\
+    python -m scaffold_b200.analysis.corpus --sweep-json out/sweep.json \\
         --out scaffold_b200/analysis/data/scaffold_corpus_scale7_b200.json
 
 Role of the reference: triton_conv3d/tests/data/scaffold_corpus.json and the make_corpus tooling around it.
