@@ -7,6 +7,8 @@ import csv
 import faulthandler
 import os
 import sys
+
+sys.path.insert(0, os.path.abspath(os.path.join(os.path.dirname(__file__), "..", "..", "..")))  # repo root: runnable directly
 from pathlib import Path
 
 import yaml

@@ -2,6 +2,8 @@
 import os
 import sys
 
+sys.path.insert(0, os.path.abspath(os.path.join(os.path.dirname(__file__), "..", "..", "..")))  # repo root: runnable directly
+
 import torch
 import torch.distributed as dist
 

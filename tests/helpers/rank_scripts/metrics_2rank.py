@@ -3,8 +3,12 @@
 Five validation samples over two replicas (3 + 2, no padding): each rank evaluates its own samples, the
 sample-weighted sums are all-reduced as the trainer does, and rank 0 compares with evaluating all five alone.
 """
-import faulthandler
 import os
+import sys
+
+sys.path.insert(0, os.path.abspath(os.path.join(os.path.dirname(__file__), "..", "..", "..")))  # repo root: runnable directly
+
+import faulthandler
 
 import torch
 import torch.distributed as dist

@@ -7,6 +7,8 @@ over the shards. Rank 0 then repeats the step on the whole volume without shardi
 import os
 import sys
 
+sys.path.insert(0, os.path.abspath(os.path.join(os.path.dirname(__file__), "..", "..", "..")))  # repo root: runnable directly
+
 import torch
 import torch.distributed as dist
 
