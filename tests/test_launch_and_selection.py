@@ -55,6 +55,12 @@ def test_kernel_selection_walks_shapes_without_memory_or_launches():
     assert by["down_list.0.double_conv.3"] == {"layer": "down_list.0.double_conv.3", "op": "conv k3 64->64",
                                                "input": "2x128x128x128", "fwd": "conv_plane3", "dgrad": "conv_plane3",
                                                "wgrad": "wgrad_plane", "halo": "-"}
+    # layers with >= 128 output rows run on SM pairs; a 128 -> 64 layer does so only in backward-data (rows = C_in)
+    assert by["down_list.2.maxpool_conv.1.double_conv.3"]["fwd"] == "conv_plane2(pair)"
+    assert by["down_list.2.maxpool_conv.1.double_conv.3"]["dgrad"] == "conv_plane2(pair)"
+    assert by["up_list.3.conv.double_conv.0"]["fwd"] == "conv_plane3"
+    assert by["up_list.3.conv.double_conv.0"]["dgrad"] == "conv_plane2(pair)"
+    assert by["down_list.1.maxpool_conv.1.double_conv.0"]["dgrad"] == "conv_plane3"   # 64 rows
     assert by["down_list.4.maxpool_conv.1.double_conv.0"]["fwd"] == "conv_small"
     assert by["up_list.0.up"]["op"] == "convT k2 1024->512" and by["up_list.4.conv"]["fwd"] == "igemm"
     assert by["down_list.0.double_conv.0"]["fwd"].startswith("conv_plane3 (32-ch")
