@@ -35,3 +35,48 @@ def test_partition_helpers_are_exact_on_large_extents():
     for sid in range(8):
         cover.add(tuple((v.start, v.stop) for v in spatial_slices((512, 512, 512), (2, 2, 2), (2, 3, 4), sid)))
     assert len(cover) == 8
+
+
+def _pair_jobs(n, d, h, w, cout_pad, bn, td):
+    """Python restatement of the pair kernel's job decode (csrc/conv_plane2.cu:decode_job2): which
+    (sample, depth group, h tile, w tile, channel tile) CTA `rank` of pair-job `pj` works on."""
+    tiles_h, tiles_w, groups_d = -(-h // 8), -(-w // 16), -(-d // td)
+    tiles_co = cout_pad // bn
+    tiles = n * groups_d * tiles_h * tiles_w
+    num_pair_jobs = ((tiles + 1) // 2) * tiles_co
+    for pj in range(num_pair_jobs):
+        co = pj % tiles_co
+        for rank in (0, 1):
+            t = (pj // tiles_co) * 2 + rank
+            wt = t % tiles_w; t //= tiles_w
+            ht = t % tiles_h; t //= tiles_h
+            dg = t % groups_d; t //= groups_d
+            yield pj, rank, (t, dg, ht, wt, co)
+
+
+@pytest.mark.parametrize("shape", [(2, 64, 64, 64, 128, 128, 4), (1, 5, 16, 16, 256, 256, 2), (1, 3, 8, 16, 128, 128, 2),
+                                   (3, 7, 24, 40, 512, 256, 1), (1, 1, 8, 32, 384, 128, 1)])
+def test_pair_kernel_jobs_cover_every_tile_once_and_statistics_slots_are_unique(shape):
+    n, d, h, w, cout_pad, bn, td = shape
+    tiles_h, tiles_w, groups_d = -(-h // 8), -(-w // 16), -(-d // td)
+    seen, spare = set(), 0
+    slots = set()
+    splits = groups_d * tiles_h * tiles_w * 4
+    for pj, rank, (smp, dg, ht, wt, co) in _pair_jobs(n, d, h, w, cout_pad, bn, td):
+        if smp >= n:                      # the odd tile out: its loads read the fill value, its stores are masked
+            spare += 1
+            assert rank == 1 and smp == n and (dg, ht, wt) == (0, 0, 0)
+            continue
+        key = (smp, dg, ht, wt, co)
+        assert key not in seen
+        seen.add(key)
+        for q in range(4):                # one GroupNorm partial per epilogue warp of the tile
+            sj = ((dg * tiles_h + ht) * tiles_w + wt) * 4 + q
+            assert 0 <= sj < splits
+            slots.add((smp, sj, co))
+    tiles = n * groups_d * tiles_h * tiles_w
+    assert len(seen) == tiles * (cout_pad // bn)
+    assert spare == (tiles % 2) * (cout_pad // bn)
+    assert len(slots) == len(seen) * 4    # no two (tile, warp) pairs share a slot of a channel tile
+    # the widest offsets stay inside 64-bit voxel arithmetic and the 32-bit tile counters
+    assert tiles * (cout_pad // bn) < 2 ** 31
