@@ -1,6 +1,7 @@
 """Shapes whose element offsets pass 2^31: the cost model flags them, the index arithmetic the kernels use
 (64-bit voxel offsets, 32-bit per-axis TMA coordinates) holds them, and the partition helpers stay exact."""
 import numpy as np
+import pytest
 
 from scaffold_b200.analysis.shapes import ConvProblem, edge_cases
 from scaffold_b200.utils.sharding import chunk_slice, spatial_slices
