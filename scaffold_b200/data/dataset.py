@@ -196,7 +196,10 @@ class FractalDataset(Dataset):
 
     @staticmethod
     def _to_mask_carrier(mask: np.ndarray) -> torch.Tensor:
-        return torch.from_numpy(np.ascontiguousarray(mask.astype(np.int16, copy=False)))
+        mask = np.ascontiguousarray(mask.astype(np.int16, copy=False))
+        if not mask.flags.writeable:  # a memory-mapped int16 mask read whole: detach it from the file
+            mask = mask.copy()
+        return torch.from_numpy(mask)
 
     def load_mask_only(self, idx: int) -> torch.Tensor:
         return self._to_mask_carrier(self._load_mask(self.ids[idx]))
@@ -210,4 +213,6 @@ class FractalDataset(Dataset):
             sl = self._slices(img.shape[-3:])
             img = img[(slice(None), *sl)]
         img = np.ascontiguousarray(img, dtype=np.float32)
+        if not img.flags.writeable:  # still the read-only memory map (whole-volume file, nothing cut off): detach it
+            img = img.copy()
         return {"image": torch.from_numpy(img), "mask": self._to_mask_carrier(self._load_mask(ident))}
