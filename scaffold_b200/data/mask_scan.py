@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import argparse
 import pickle
-from multiprocessing import Pool
+import multiprocessing
 from pathlib import Path
 from typing import List
 
@@ -23,7 +23,8 @@ def scan(masks_dir, workers: int = 4) -> List[int]:
     if not files:
         raise FileNotFoundError(f"no .npy masks under {masks_dir}")
     if workers > 1:
-        with Pool(workers) as pool:
+        # "spawn": the caller may be multi-threaded (a fork of such a process can deadlock in the child)
+        with multiprocessing.get_context("spawn").Pool(workers) as pool:
             parts = pool.map(unique_values, files)
     else:
         parts = [unique_values(f) for f in files]
