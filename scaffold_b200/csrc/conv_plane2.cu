@@ -20,7 +20,9 @@
 // word; a CTA leaves only after a cluster barrier, so no arrive can land in a CTA that is gone.
 //
 // Features are those of the single-CTA plane kernel: two concatenated sources, the fused depth
-// halo (landing slabs + flag words), slab outputs for backward-data.
+// halo (landing slabs + flag words), slab outputs for backward-data; the forward instantiation
+// can also leave GroupNorm partial statistics of what it stores (one partial per epilogue warp).
+// Tile width (128 / 256) and job depth come from a cost model fitted to measurements (p2_choose).
 // Role of the reference: triton_conv3d/gather_gemm.py:112-341 and bwd_data.py:275-363.
 #include "common.cuh"
 #include "host_api.h"
