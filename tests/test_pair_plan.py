@@ -58,3 +58,24 @@ def test_pair_plan_depth_never_exceeds_the_volume_or_tmem():
             assert got is not None
             bn, td = got
             assert td * bn <= 512 and (td <= d or td == 1) and cout % bn == 0
+
+
+@pytest.mark.parametrize("bn,cg", [(128, 16), (128, 32), (128, 64), (128, 128), (256, 16), (256, 32), (256, 64),
+                                   (256, 128), (256, 256)])
+def test_statistics_epilogue_maps_every_16_channel_half_to_its_group(bn, cg):
+    """Python restatement of the epilogue's group arithmetic (csrc/conv_plane2.cu): the job's BN columns arrive as
+    chunks of 32 split in halves of 16; half (chunk, g) belongs to local group (chunk * 32 + g * 16) // cg. Every
+    column must land in the group that holds its channel, and the groups of a tile must be <= 16."""
+    groups_here = bn // cg
+    assert 1 <= groups_here <= 16 and cg % 16 == 0
+    cols_per_group = [0] * groups_here
+    for chunk in range(bn // 32):
+        for g in range(2):
+            gl = (chunk * 32 + g * 16) // cg
+            first, last = chunk * 32 + g * 16, chunk * 32 + g * 16 + 15
+            assert first // cg == gl == last // cg          # a half never straddles two groups
+            cols_per_group[gl] += 16
+    assert cols_per_group == [cg] * groups_here
+    # global group index of local group l in the channel tile that starts at co0: co0 // cg + l
+    for co0 in (0, bn, 3 * bn):
+        assert [(co0 + l * cg) // cg for l in range(groups_here)] == [co0 // cg + l for l in range(groups_here)]
