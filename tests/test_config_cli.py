@@ -145,3 +145,14 @@ def test_cli_flags_for_the_fused_paths_reach_the_config(tmp_path):
                             "--halo-exchange", "nccl", "--dc-num-shards", "1", "1", "2"])
     assert ns.grad_overlap == 0 and ns.allow_fallback == 1 and ns.halo_exchange == "nccl"
     assert ns.dc_num_shards == [1, 1, 2]
+
+
+def test_validation_cache_budget_flag_parses_as_a_number(tmp_path):
+    base = tmp_path / "b.yml"
+    base.write_text(yaml.safe_dump(base_dict(tmp_path, problem_scale=5)))
+    ns = cli.build_parser().parse_args(["benchmark", "-c", str(base), "--val-cache-gb", "0.5"])
+    assert ns.val_cache_gb == 0.5
+    assert C.Config(base_dict(tmp_path, val_cache_gb=ns.val_cache_gb)).val_cache_gb == 0.5
+    assert C.Config(base_dict(tmp_path, val_cache_gb=2)).val_cache_gb == 2.0      # an integer in the YAML is fine
+    with pytest.raises(ValueError, match="non-negative number"):
+        C.Config(base_dict(tmp_path, val_cache_gb=True))                          # a boolean is a typo here
